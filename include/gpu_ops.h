@@ -1,0 +1,202 @@
+/*
+ * gpu_ops.h -- C ABI of libgpu_ops.so: the attention hot path of llm_simple
+ * (RoPE, KV-cache append, causal prefill attention, grouped-query decode) as
+ * hand-written CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point replaces one operator of the reference's
+ * prebuild/npu_ops.h (cited per function) or is a fused form of several.
+ * Differences from the reference's calling convention, all deliberate:
+ *   - C linkage; the stream is a cudaStream_t passed by value as an opaque
+ *     pointer (the reference passes `aclrtStream&`);
+ *   - every function returns an int status: 0 on success, a negative
+ *     GPU_OPS_E_* code otherwise (the reference returns void and logs);
+ *     gpu_ops_last_error_string() describes the last failure of the calling
+ *     thread;
+ *   - all arguments are validated on the host before anything is launched; no
+ *     kernel traps or asserts;
+ *   - `dt` is the reference's DataType value: 4 = fp16, 5 = bf16
+ *     (prebuild/defs.hpp:8-18).  Accumulation is always fp32.
+ *
+ * All pointers are device pointers unless a parameter is documented as host
+ * memory.  Calls are asynchronous on `stream`.  head_dim must be 128 (every
+ * model the reference supports has head_dim 128); other values are rejected
+ * with GPU_OPS_E_UNSUPPORTED.
+ */
+#ifndef LLM_SIMPLE_GPU_OPS_H_
+#define LLM_SIMPLE_GPU_OPS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *gpu_stream_t; /* a cudaStream_t; NULL is the default stream */
+
+enum {
+  GPU_OPS_OK = 0,
+  GPU_OPS_E_INVALID = -1,     /* null pointer, non-positive extent, inconsistent arguments */
+  GPU_OPS_E_UNSUPPORTED = -2, /* dtype / head_dim / shape outside what the kernels cover */
+  GPU_OPS_E_WORKSPACE = -3,   /* workspace missing or too small */
+  GPU_OPS_E_CUDA = -4         /* a CUDA runtime call or launch failed */
+};
+
+enum { GPU_DT_FLOAT16 = 4, GPU_DT_BFLOAT16 = 5 };
+
+/* ------------------------------------------------------------------------
+ * Reference-shaped operators.  Same argument order and meaning as the
+ * reference; K/V are token-major [n][kv_heads][head_dim] (the layout of the
+ * reference's caches, src/llama2_layer_npu.cpp:325-338, :1148-1149).
+ * ------------------------------------------------------------------------ */
+
+/* Replaces npu_flash_attn_layer (prebuild/npu_ops.h:6-8).
+ * q [m][head_num][head_dim], k/v [n][head_num][head_dim] (first n rows valid),
+ * out [m][head_num*head_dim].  Row r attends to columns c <= r + offset
+ * (tests/flash_attn_test.cpp:124-132); scale 1/sqrt(head_dim). */
+int gpu_flash_attn_layer(void *output_dev, const void *q_dev, const void *k_dev,
+                         const void *v_dev, int m, int n, int offset, int head_num,
+                         int head_dim, int dt, gpu_stream_t stream);
+
+/* Replaces npu_flash_attn_gqa_layer (prebuild/npu_ops.h:10-13).
+ * q [m][kv_head_num*group_size][head_dim], k/v [n][kv_head_num][head_dim];
+ * query head h reads KV head h / group_size (call site
+ * src/llama2_layer_npu.cpp:866-869). */
+int gpu_flash_attn_gqa_layer(void *output_dev, const void *q_dev, const void *k_dev,
+                             const void *v_dev, int m, int n, int offset, int group_size,
+                             int kv_head_num, int head_dim, int dt, gpu_stream_t stream);
+
+/* Replaces npu_flash_attn_opt_prefill_layer (prebuild/npu_ops.h:15-18); the
+ * reference uses it for prefill and for decode (m = 1) alike
+ * (src/llama2_layer_npu.cpp:371-374).  Same contract as gpu_flash_attn_layer. */
+int gpu_flash_attn_opt_prefill_layer(void *output_dev, const void *q_dev, const void *k_dev,
+                                     const void *v_dev, int m, int n, int offset,
+                                     int head_num, int head_dim, int dt, gpu_stream_t stream);
+
+/* Replaces npu_rope_layer (prebuild/npu_ops.h:39-42): rotates Q and K
+ * ([cur_size][n_heads][hidden_dim/n_heads] each) with table rows
+ * start_pos .. start_pos+cur_size-1.  freqs_cis is fp32 [max_seq][D/2][2] =
+ * (cos, sin) as built by ModelBase::InitFreqCIS (src/model_base.cpp:27-83).
+ * Pairs are (2f, 2f+1), or (f, f+D/2) when is_neox_style != 0
+ * (tests/rope_single_layer_test.cpp:86-91).  Results are bit-identical to the
+ * reference tests' golden: fp32 products, one subtraction / addition, one
+ * rounding to the dtype. */
+int gpu_rope_layer(void *output_q_dev, void *output_k_dev, const void *freqs_cis_dev,
+                   const void *input_q_dev, const void *input_k_dev, int start_pos,
+                   int cur_size, int n_heads, int hidden_dim, int is_neox_style, int dt,
+                   gpu_stream_t stream);
+
+/* Replaces npu_rope_single_layer (prebuild/npu_ops.h:44-47); hidden_dim is
+ * n_heads*head_dim of the tensor being rotated (src/llama2_layer_npu.cpp:790-798). */
+int gpu_rope_single_layer(void *output_x_dev, const void *freqs_cis_dev,
+                          const void *input_x_dev, int start_pos, int cur_size, int n_heads,
+                          int hidden_dim, int is_neox_style, int dt, gpu_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Fused operators: the same path with a batch dimension, explicit strides
+ * (token-major and head-major caches) and RoPE + append in the same pass.
+ * ------------------------------------------------------------------------ */
+
+/* Geometry shared by the fused operators.  All strides are in ELEMENTS.
+ *   q / out element (seq b, token t, head h, d):  b*seq_stride + t*tok_stride + h*head_dim + d
+ *   raw k / v input element (b, t, kv_head, d):   b*kv_in_seq_stride + t*kv_in_tok_stride + kv_head*head_dim + d
+ *   cache element (b, kv_head, pos, d):           b*cache_seq_stride + kv_head*cache_head_stride + pos*cache_pos_stride + d
+ * The K and V caches have the same geometry.  Token-major (reference) cache:
+ * head_stride = head_dim, pos_stride = n_kv_heads*head_dim.  Head-major cache
+ * [kv_head][max_pos][head_dim]: head_stride = max_pos*head_dim, pos_stride = head_dim.
+ * cache_pos_stride and cache_head_stride must be multiples of 8 elements. */
+typedef struct gpu_attn_desc {
+  int32_t dtype;         /* GPU_DT_FLOAT16 / GPU_DT_BFLOAT16 */
+  int32_t batch;         /* independent sequences */
+  int32_t n_heads;       /* query heads = n_kv_heads * group size */
+  int32_t n_kv_heads;
+  int32_t head_dim;      /* 128 */
+  int32_t is_neox_style; /* RoPE pairing */
+  int64_t q_seq_stride, q_tok_stride;
+  int64_t kv_in_seq_stride, kv_in_tok_stride;
+  int64_t out_seq_stride, out_tok_stride;
+  int64_t cache_seq_stride, cache_head_stride, cache_pos_stride;
+} gpu_attn_desc;
+
+/* RoPE(Q) -> q_out, RoPE(K) -> k_cache, V -> v_cache for m new tokens of every
+ * sequence, in one pass.  Fuses npu_rope_layer / 2 x npu_rope_single_layer with
+ * the two cache-append copies (src/llama2_layer_npu.cpp:284, :325-338;
+ * :790-798, :830-843).  start_pos_dev: int32 [batch], tokens already cached
+ * (= table row of the first new token); if NULL, `start_pos` is used for all.
+ * q_out may alias q_in. */
+int gpu_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cache,
+                             void *v_cache, const void *q_in, const void *k_in,
+                             const void *v_in, const void *freqs_cis_dev,
+                             const int32_t *start_pos_dev, int start_pos, int m,
+                             gpu_stream_t stream);
+
+/* Causal attention of m new (already rotated) query rows per sequence over
+ * cache positions [0, offset + m); row r sees positions <= offset + r.  The
+ * batched, strided form of gpu_flash_attn_gqa_layer. */
+int gpu_attn_prefill_layer(const gpu_attn_desc *desc, void *out, const void *q,
+                           const void *k_cache, const void *v_cache, int m, int offset,
+                           gpu_stream_t stream);
+
+/* One fused decode step for every sequence: rotate the new token's Q and K,
+ * append K and V at cache position kv_len[b], attend over positions
+ * [0, kv_len[b]] with the cache split into chunks, merge the chunks.
+ *   q_in [batch][n_heads][D], k_in/v_in [batch][n_kv_heads][D]: raw (unrotated)
+ *   kv_len_dev   int32 [batch]: tokens already in the cache of sequence b
+ *   rope_pos_dev int32 [batch] or NULL: table row used for the rotation
+ *                (NULL: kv_len[b]); differs from kv_len when the cache holds
+ *                only a slice of the sequence
+ *   append_new   1: append and attend to the new token; 0: attend to
+ *                [0, kv_len[b]) only and leave the cache untouched (k_in/v_in
+ *                may be NULL)
+ *   max_kv_len   host upper bound of kv_len[b] + append_new over the batch (sizes the grid)
+ *   workspace    device scratch of at least gpu_attn_decode_workspace_bytes()
+ * Output: out [batch][n_heads*D] in the dtype; if o_partial/lse_partial are not
+ * NULL the kernel instead writes the normalised fp32 result [batch][n_heads][D]
+ * and its log-sum-exp [batch][n_heads] (natural log; -inf for an empty slice),
+ * for a merge across devices with gpu_attn_merge_lse_layer. */
+int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial,
+                          float *lse_partial, const void *q_in, const void *k_in,
+                          const void *v_in, void *k_cache, void *v_cache,
+                          const void *freqs_cis_dev, const int32_t *kv_len_dev,
+                          const int32_t *rope_pos_dev, int append_new, int max_kv_len,
+                          void *workspace, size_t workspace_bytes, gpu_stream_t stream);
+
+/* Scratch bytes gpu_attn_decode_layer needs for this geometry and bound. */
+size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len);
+
+/* Merge n_parts partial results: o_parts fp32 [n_parts][rows][head_dim]
+ * (normalised), lse_parts fp32 [n_parts][rows] (natural log).
+ * out[row] = sum_p exp(lse_p - M) o_p / sum_p exp(lse_p - M), M = max_p lse_p,
+ * written in the dtype as [rows][head_dim]. */
+int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_parts,
+                             int n_parts, int rows, int head_dim, int dt,
+                             gpu_stream_t stream);
+
+/* Scratch for the reference-shaped attention operators on the CURRENT device.
+ * They take no workspace argument (the reference's signatures have none) and
+ * never allocate; with scratch registered, decode-shaped calls (m * group_size
+ * <= 16) split long caches across CTAs, without it they run unsplit.  The
+ * library keeps the pointer, not the memory: pass NULL before freeing it.
+ * Calls that share the scratch must be ordered on one stream. */
+int gpu_ops_set_workspace(void *workspace, size_t bytes);
+
+/* Positions per split used by gpu_attn_decode_layer; 0 restores the built-in
+ * choice.  A multiple of 64.  Process-wide tuning knob. */
+int gpu_attn_set_decode_chunk(int positions);
+
+/* Which kernel gpu_attn_prefill_layer and the reference-shaped operators use
+ * for rows beyond the small-m path: 0 = automatic, 1 = mma.sync kernel,
+ * 2 = tcgen05 kernel.  Process-wide; for tests and measurements. */
+int gpu_attn_set_prefill_kernel(int which);
+
+/* Number of kernels launched by this library on the calling thread since the
+ * last call with reset != 0. */
+long gpu_ops_launch_count(int reset);
+
+/* Description of the last non-zero status returned on the calling thread. */
+const char *gpu_ops_last_error_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLM_SIMPLE_GPU_OPS_H_ */

@@ -1,0 +1,462 @@
+// C ABI of libgpu_ops.so (declared in include/gpu_ops.h): argument validation
+// on the host, geometry set-up and kernel dispatch.  No entry point allocates
+// device memory.
+#include "gpu_ops.h"
+#include "kernels.h"
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+using namespace b200attn;
+
+namespace {
+
+thread_local std::string g_last_error;
+thread_local long g_launches = 0;
+std::atomic<int> g_decode_chunk{0};
+std::atomic<int> g_prefill_kernel{0};
+
+// caller-registered scratch for the reference-shaped operators, per device
+struct RegisteredWorkspace {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+std::mutex g_ws_mutex;
+RegisteredWorkspace g_ws[64];
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  return fail(GPU_OPS_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool dt_ok(int dt) { return dt == GPU_DT_FLOAT16 || dt == GPU_DT_BFLOAT16; }
+
+int check_common(int dt, int head_dim) {
+  if (!dt_ok(dt)) return fail(GPU_OPS_E_UNSUPPORTED, "dtype %d: only fp16 (4) and bf16 (5) are supported", dt);
+  if (head_dim != 128) return fail(GPU_OPS_E_UNSUPPORTED, "head_dim %d: only 128 is supported", head_dim);
+  return GPU_OPS_OK;
+}
+
+int check_desc(const gpu_attn_desc *d) {
+  if (!d) return fail(GPU_OPS_E_INVALID, "desc is NULL");
+  if (int rc = check_common(d->dtype, d->head_dim)) return rc;
+  if (d->batch <= 0 || d->n_heads <= 0 || d->n_kv_heads <= 0 || d->n_heads % d->n_kv_heads)
+    return fail(GPU_OPS_E_INVALID, "batch %d, n_heads %d, n_kv_heads %d", d->batch, d->n_heads, d->n_kv_heads);
+  if (d->cache_pos_stride % 8 || d->cache_head_stride % 8 || d->cache_seq_stride % 8 || d->q_tok_stride % 8 ||
+      d->q_seq_stride % 8 || d->kv_in_tok_stride % 8 || d->kv_in_seq_stride % 8 || d->out_tok_stride % 8 ||
+      d->out_seq_stride % 8)
+    return fail(GPU_OPS_E_INVALID, "strides must be multiples of 8 elements (16-byte accesses)");
+  return GPU_OPS_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+AttnGeom geom_from_desc(const gpu_attn_desc *d) {
+  AttnGeom g{};
+  g.batch = d->batch;
+  g.n_heads = d->n_heads;
+  g.n_kv_heads = d->n_kv_heads;
+  g.group = d->n_heads / d->n_kv_heads;
+  g.q_seq = d->q_seq_stride;
+  g.q_tok = d->q_tok_stride;
+  g.out_seq = d->out_seq_stride;
+  g.out_tok = d->out_tok_stride;
+  g.c_seq = d->cache_seq_stride;
+  g.c_head = d->cache_head_stride;
+  g.c_pos = d->cache_pos_stride;
+  return g;
+}
+
+float scale_log2_of(int head_dim) {
+  return (1.0f / sqrtf(static_cast<float>(head_dim))) * 1.4426950408889634f;
+}
+
+// Positions per split: enough CTAs to fill 148 SMs x 2 resident CTAs several
+// times over, but no split shorter than 256 positions (128 KB of K+V).
+int pick_chunk(int units, int max_len) {
+  int forced = g_decode_chunk.load();
+  if (forced > 0) return forced;
+  const long want_ctas = 148L * 2 * 8;
+  long per_unit = (want_ctas + units - 1) / units;
+  if (per_unit < 1) per_unit = 1;
+  long chunk = (max_len + per_unit - 1) / per_unit;
+  chunk = ((chunk + 63) / 64) * 64;
+  if (chunk < 256) chunk = 256;
+  return static_cast<int>(chunk);
+}
+
+size_t decode_ws_bytes(long rows, int splits) {
+  return static_cast<size_t>(rows) * splits * (128 + 1) * sizeof(float);
+}
+
+// q rows handled by the split decode kernel: m * group <= 16
+bool small_m(int m, int group) { return static_cast<long>(m) * group <= 16; }
+
+int run_prefill(const PrefillParams &p, bool bf16, cudaStream_t stream) {
+  const int which = g_prefill_kernel.load();
+  cudaError_t e;
+  if (which != 1) {
+    e = launch_attn_prefill_tc5(p, bf16, stream);
+    if (e == cudaSuccess) {
+      g_launches += 1;
+      return GPU_OPS_OK;
+    }
+    if (e != cudaErrorNotSupported || which == 2) return cuda_fail(e, "tcgen05 prefill attention launch");
+    (void)cudaGetLastError();
+  }
+  e = launch_attn_prefill_mma(p, bf16, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "prefill attention launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+int ref_attention(void *out, const void *q, const void *k, const void *v, int m, int n, int offset, int group,
+                  int kv_heads, int head_dim, int dt, gpu_stream_t stream) {
+  if (int rc = check_common(dt, head_dim)) return rc;
+  if (!out || !q || !k || !v) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (m <= 0 || n <= 0 || offset < 0 || group <= 0 || kv_heads <= 0)
+    return fail(GPU_OPS_E_INVALID, "m %d, n %d, offset %d, group_size %d, kv_head_num %d", m, n, offset, group,
+                kv_heads);
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k) || !aligned16(v))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  const bool bf16 = dt == GPU_DT_BFLOAT16;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  AttnGeom g{};
+  g.batch = 1;
+  g.n_kv_heads = kv_heads;
+  g.group = group;
+  g.n_heads = kv_heads * group;
+  g.q_tok = g.out_tok = static_cast<long>(g.n_heads) * head_dim;
+  g.q_seq = g.out_seq = 0;
+  g.c_seq = 0;
+  g.c_head = head_dim;
+  g.c_pos = static_cast<long>(kv_heads) * head_dim;
+  if (small_m(m, group)) {
+    DecodeParams p{};
+    p.g = g;
+    p.out = out;
+    p.q = q;
+    p.k_cache = const_cast<void *>(k);
+    p.v_cache = const_cast<void *>(v);
+    p.kv_len = n;
+    p.m = m;
+    p.offset = offset;
+    p.scale_log2 = scale_log2_of(head_dim);
+    // split only if the caller registered scratch for this device
+    p.chunk = ((n + 63) / 64) * 64;
+    p.max_splits = 1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+      std::lock_guard<std::mutex> lk(g_ws_mutex);
+      if (dev >= 0 && dev < 64 && g_ws[dev].ptr) {
+        const int chunk = pick_chunk(kv_heads, n);
+        const int splits = (n + chunk - 1) / chunk;
+        const long rows = static_cast<long>(m) * g.n_heads;
+        if (splits > 1 && decode_ws_bytes(rows, splits) <= g_ws[dev].bytes) {
+          p.chunk = chunk;
+          p.max_splits = splits;
+          p.ws_o = static_cast<float *>(g_ws[dev].ptr);
+          p.ws_lse = p.ws_o + rows * splits * 128;
+        }
+      }
+    }
+    int launches = 0;
+    cudaError_t e = launch_attn_decode(p, bf16, s, &launches);
+    g_launches += launches;
+    if (e != cudaSuccess) return cuda_fail(e, "decode attention launch");
+    return GPU_OPS_OK;
+  }
+  PrefillParams p{};
+  p.g = g;
+  p.out = out;
+  p.q = q;
+  p.k_cache = k;
+  p.v_cache = v;
+  p.m = m;
+  p.n = n;
+  p.offset = offset;
+  p.scale_log2 = scale_log2_of(head_dim);
+  return run_prefill(p, bf16, s);
+}
+
+int ref_rope(void *out_q, void *out_k, const void *freqs, const void *in_q, const void *in_k, int start_pos,
+             int cur_size, int n_heads, int hidden_dim, int is_neox, int dt, gpu_stream_t stream) {
+  if (!dt_ok(dt)) return fail(GPU_OPS_E_UNSUPPORTED, "dtype %d: only fp16 (4) and bf16 (5) are supported", dt);
+  if (n_heads <= 0 || hidden_dim <= 0 || hidden_dim % n_heads)
+    return fail(GPU_OPS_E_INVALID, "n_heads %d, hidden_dim %d", n_heads, hidden_dim);
+  if (hidden_dim / n_heads != 128)
+    return fail(GPU_OPS_E_UNSUPPORTED, "head_dim %d: only 128 is supported", hidden_dim / n_heads);
+  if (!out_q || !freqs || !in_q || (out_k && !in_k)) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (start_pos < 0 || cur_size < 0) return fail(GPU_OPS_E_INVALID, "start_pos %d, cur_size %d", start_pos, cur_size);
+  if (!aligned16(out_q) || !aligned16(in_q) || !aligned16(out_k) || !aligned16(in_k) || !aligned16(freqs))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  if (cur_size == 0) return GPU_OPS_OK;
+  RopeParams p{};
+  auto set = [&](RopeStream &st, const void *src, void *dst) {
+    st.src = src;
+    st.dst = dst;
+    st.heads = n_heads;
+    st.rotate = 1;
+    st.dst_at_pos = 0;
+    st.src_seq = st.dst_seq = 0;
+    st.src_tok = st.dst_tok = hidden_dim;
+    st.dst_head = 128;
+  };
+  set(p.s[0], in_q, out_q);
+  p.slots = n_heads;
+  if (out_k) {
+    set(p.s[1], in_k, out_k);
+    p.slots += n_heads;
+  }
+  p.freqs_cis = static_cast<const float *>(freqs);
+  p.start_pos = start_pos;
+  p.batch = 1;
+  p.m = cur_size;
+  p.is_neox = is_neox ? 1 : 0;
+  cudaError_t e = launch_rope_append(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "rope launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int gpu_flash_attn_layer(void *output_dev, const void *q_dev, const void *k_dev, const void *v_dev, int m, int n,
+                         int offset, int head_num, int head_dim, int dt, gpu_stream_t stream) {
+  return ref_attention(output_dev, q_dev, k_dev, v_dev, m, n, offset, 1, head_num, head_dim, dt, stream);
+}
+
+int gpu_flash_attn_gqa_layer(void *output_dev, const void *q_dev, const void *k_dev, const void *v_dev, int m,
+                             int n, int offset, int group_size, int kv_head_num, int head_dim, int dt,
+                             gpu_stream_t stream) {
+  return ref_attention(output_dev, q_dev, k_dev, v_dev, m, n, offset, group_size, kv_head_num, head_dim, dt, stream);
+}
+
+int gpu_flash_attn_opt_prefill_layer(void *output_dev, const void *q_dev, const void *k_dev, const void *v_dev,
+                                     int m, int n, int offset, int head_num, int head_dim, int dt,
+                                     gpu_stream_t stream) {
+  return ref_attention(output_dev, q_dev, k_dev, v_dev, m, n, offset, 1, head_num, head_dim, dt, stream);
+}
+
+int gpu_rope_layer(void *output_q_dev, void *output_k_dev, const void *freqs_cis_dev, const void *input_q_dev,
+                   const void *input_k_dev, int start_pos, int cur_size, int n_heads, int hidden_dim,
+                   int is_neox_style, int dt, gpu_stream_t stream) {
+  if (!output_k_dev || !input_k_dev) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  return ref_rope(output_q_dev, output_k_dev, freqs_cis_dev, input_q_dev, input_k_dev, start_pos, cur_size, n_heads,
+                  hidden_dim, is_neox_style, dt, stream);
+}
+
+int gpu_rope_single_layer(void *output_x_dev, const void *freqs_cis_dev, const void *input_x_dev, int start_pos,
+                          int cur_size, int n_heads, int hidden_dim, int is_neox_style, int dt,
+                          gpu_stream_t stream) {
+  return ref_rope(output_x_dev, nullptr, freqs_cis_dev, input_x_dev, nullptr, start_pos, cur_size, n_heads,
+                  hidden_dim, is_neox_style, dt, stream);
+}
+
+int gpu_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cache, void *v_cache, const void *q_in,
+                             const void *k_in, const void *v_in, const void *freqs_cis_dev,
+                             const int32_t *start_pos_dev, int start_pos, int m, gpu_stream_t stream) {
+  if (int rc = check_desc(desc)) return rc;
+  if (!k_cache || !v_cache || !k_in || !v_in || !freqs_cis_dev || (q_out && !q_in))
+    return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (m < 0 || (!start_pos_dev && start_pos < 0)) return fail(GPU_OPS_E_INVALID, "m %d, start_pos %d", m, start_pos);
+  if (!aligned16(q_out) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(q_in) || !aligned16(k_in) ||
+      !aligned16(v_in) || !aligned16(freqs_cis_dev))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  if (m == 0) return GPU_OPS_OK;
+  RopeParams p{};
+  int slots = 0;
+  if (q_out) {
+    RopeStream &s = p.s[slots];
+    s.src = q_in;
+    s.dst = q_out;
+    s.heads = desc->n_heads;
+    s.rotate = 1;
+    s.dst_at_pos = 0;
+    s.src_seq = s.dst_seq = desc->q_seq_stride;
+    s.src_tok = s.dst_tok = desc->q_tok_stride;
+    s.dst_head = 128;
+    ++slots;
+  }
+  for (int kv = 0; kv < 2; ++kv) {
+    RopeStream &s = p.s[slots++];
+    s.src = kv == 0 ? k_in : v_in;
+    s.dst = kv == 0 ? k_cache : v_cache;
+    s.heads = desc->n_kv_heads;
+    s.rotate = kv == 0 ? 1 : 0;
+    s.dst_at_pos = 1;
+    s.src_seq = desc->kv_in_seq_stride;
+    s.src_tok = desc->kv_in_tok_stride;
+    s.dst_seq = desc->cache_seq_stride;
+    s.dst_tok = desc->cache_pos_stride;
+    s.dst_head = desc->cache_head_stride;
+  }
+  p.slots = (q_out ? desc->n_heads : 0) + 2 * desc->n_kv_heads;
+  p.freqs_cis = static_cast<const float *>(freqs_cis_dev);
+  p.start_pos_dev = start_pos_dev;
+  p.start_pos = start_pos;
+  p.batch = desc->batch;
+  p.m = m;
+  p.is_neox = desc->is_neox_style ? 1 : 0;
+  cudaError_t e = launch_rope_append(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "rope + append launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+int gpu_attn_prefill_layer(const gpu_attn_desc *desc, void *out, const void *q, const void *k_cache,
+                           const void *v_cache, int m, int offset, gpu_stream_t stream) {
+  if (int rc = check_desc(desc)) return rc;
+  if (!out || !q || !k_cache || !v_cache) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (m <= 0 || offset < 0) return fail(GPU_OPS_E_INVALID, "m %d, offset %d", m, offset);
+  if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  PrefillParams p{};
+  p.g = geom_from_desc(desc);
+  p.out = out;
+  p.q = q;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.m = m;
+  p.n = offset + m;
+  p.offset = offset;
+  p.scale_log2 = scale_log2_of(desc->head_dim);
+  return run_prefill(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+}
+
+size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len) {
+  if (!desc || desc->batch <= 0 || desc->n_kv_heads <= 0 || max_kv_len <= 0) return 0;
+  const int chunk = pick_chunk(desc->batch * desc->n_kv_heads, max_kv_len);
+  const int splits = (max_kv_len + chunk - 1) / chunk;
+  return decode_ws_bytes(static_cast<long>(desc->batch) * desc->n_heads, splits);
+}
+
+int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial, float *lse_partial,
+                          const void *q_in, const void *k_in, const void *v_in, void *k_cache, void *v_cache,
+                          const void *freqs_cis_dev, const int32_t *kv_len_dev, const int32_t *rope_pos_dev,
+                          int append_new, int max_kv_len, void *workspace, size_t workspace_bytes,
+                          gpu_stream_t stream) {
+  if (int rc = check_desc(desc)) return rc;
+  const int group = desc->n_heads / desc->n_kv_heads;
+  if (group > 16) return fail(GPU_OPS_E_UNSUPPORTED, "group size %d: at most 16 query heads per KV head", group);
+  if (!q_in || !k_cache || !v_cache || !freqs_cis_dev || !kv_len_dev)
+    return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if ((o_partial == nullptr) != (lse_partial == nullptr))
+    return fail(GPU_OPS_E_INVALID, "o_partial and lse_partial go together");
+  if (!out && !o_partial) return fail(GPU_OPS_E_INVALID, "no output given");
+  if (append_new && (!k_in || !v_in)) return fail(GPU_OPS_E_INVALID, "append_new needs k_in and v_in");
+  if (max_kv_len <= 0) return fail(GPU_OPS_E_INVALID, "max_kv_len %d", max_kv_len);
+  if (!aligned16(out) || !aligned16(q_in) || !aligned16(k_in) || !aligned16(v_in) || !aligned16(k_cache) ||
+      !aligned16(v_cache) || !aligned16(freqs_cis_dev) || !aligned16(workspace))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  DecodeParams p{};
+  p.g = geom_from_desc(desc);
+  p.out = out;
+  p.o_partial = o_partial;
+  p.lse_partial = lse_partial;
+  p.q = q_in;
+  p.k_new = k_in;
+  p.v_new = v_in;
+  p.kv_in_seq = desc->kv_in_seq_stride;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.freqs_cis = static_cast<const float *>(freqs_cis_dev);
+  p.kv_len_dev = kv_len_dev;
+  p.rope_pos_dev = rope_pos_dev;
+  p.m = 1;
+  p.offset = -1;
+  p.append = append_new ? 1 : 0;
+  p.rotate_q = 1;
+  p.is_neox = desc->is_neox_style ? 1 : 0;
+  p.chunk = pick_chunk(desc->batch * desc->n_kv_heads, max_kv_len);
+  p.max_splits = (max_kv_len + p.chunk - 1) / p.chunk;
+  p.scale_log2 = scale_log2_of(desc->head_dim);
+  if (p.max_splits > 1) {
+    const long rows = static_cast<long>(desc->batch) * desc->n_heads;
+    const size_t need = decode_ws_bytes(rows, p.max_splits);
+    if (!workspace || workspace_bytes < need)
+      return fail(GPU_OPS_E_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    p.ws_o = static_cast<float *>(workspace);
+    p.ws_lse = p.ws_o + rows * p.max_splits * 128;
+  }
+  int launches = 0;
+  cudaError_t e = launch_attn_decode(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream), &launches);
+  g_launches += launches;
+  if (e != cudaSuccess) return cuda_fail(e, "decode attention launch");
+  return GPU_OPS_OK;
+}
+
+int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_parts, int n_parts, int rows,
+                             int head_dim, int dt, gpu_stream_t stream) {
+  if (int rc = check_common(dt, head_dim)) return rc;
+  if (!out || !o_parts || !lse_parts) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (n_parts <= 0 || rows < 0) return fail(GPU_OPS_E_INVALID, "n_parts %d, rows %d", n_parts, rows);
+  MergeParams p{};
+  p.out = out;
+  p.parts_o = o_parts;
+  p.parts_lse = lse_parts;
+  p.part_major = 1;
+  p.lse_is_log2 = 0;
+  p.rows = rows;
+  p.max_parts = n_parts;
+  p.n_parts = n_parts;
+  p.rows_per_seq = rows > 0 ? rows : 1;
+  p.n_heads = rows > 0 ? rows : 1;
+  p.m = 1;
+  p.out_seq = 0;
+  p.out_tok = 0;
+  cudaError_t e = launch_attn_merge(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "merge launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+int gpu_ops_set_workspace(void *workspace, size_t bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(GPU_OPS_E_INVALID, "device index %d", dev);
+  if (workspace && !aligned16(workspace)) return fail(GPU_OPS_E_INVALID, "workspace must be 16-byte aligned");
+  std::lock_guard<std::mutex> lk(g_ws_mutex);
+  g_ws[dev].ptr = workspace;
+  g_ws[dev].bytes = workspace ? bytes : 0;
+  return GPU_OPS_OK;
+}
+
+int gpu_attn_set_decode_chunk(int positions) {
+  if (positions < 0 || positions % 64) return fail(GPU_OPS_E_INVALID, "chunk %d: a non-negative multiple of 64", positions);
+  g_decode_chunk.store(positions);
+  return GPU_OPS_OK;
+}
+
+int gpu_attn_set_prefill_kernel(int which) {
+  if (which < 0 || which > 2) return fail(GPU_OPS_E_INVALID, "prefill kernel selector %d", which);
+  g_prefill_kernel.store(which);
+  return GPU_OPS_OK;
+}
+
+long gpu_ops_launch_count(int reset) {
+  const long n = g_launches;
+  if (reset) g_launches = 0;
+  return n;
+}
+
+const char *gpu_ops_last_error_string(void) { return g_last_error.c_str(); }
+
+} // extern "C"

@@ -1,0 +1,109 @@
+// Host-visible parameter blocks and launchers of the CUDA kernels.  Internal to
+// the library: the public surface is include/gpu_ops.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200attn {
+
+// ---- RoPE + append ---------------------------------------------------------
+// One of up to three tensors handled by a rope_append launch (Q, K, V).
+struct RopeStream {
+  const void *src; // [batch][m][heads][128], strides below
+  void *dst;
+  int heads;       // 0 disables the stream
+  int rotate;      // 1: apply RoPE, 0: copy
+  int dst_at_pos;  // 1: destination token index is start_pos + t (cache), 0: t
+  long src_seq, src_tok;
+  long dst_seq, dst_tok, dst_head;
+};
+
+struct RopeParams {
+  RopeStream s[3];
+  const float *freqs_cis; // [max_seq][64][2]
+  const int32_t *start_pos_dev;
+  int start_pos;
+  int batch, m, slots; // slots = sum of heads
+  int is_neox;
+};
+
+cudaError_t launch_rope_append(const RopeParams &p, bool bf16, cudaStream_t stream);
+
+// ---- attention (shared geometry) -------------------------------------------
+struct AttnGeom {
+  int batch, n_heads, n_kv_heads, group;
+  long q_seq, q_tok;       // rotated or raw q
+  long out_seq, out_tok;
+  long c_seq, c_head, c_pos; // cache strides (K and V alike)
+};
+
+// ---- small-m / decode kernel (split-KV, mma.sync) ----------------------------
+struct DecodeParams {
+  AttnGeom g;
+  void *out;            // dtype [batch][m][H*128] (strided) when final
+  float *o_partial;     // optional fp32 final [batch*m*H][128] + lse_partial (natural log)
+  float *lse_partial;
+  const void *q;        // raw (rotate_q) or rotated
+  const void *k_new;    // raw new-token K/V (append)
+  const void *v_new;
+  long kv_in_seq;       // stride between sequences of k_new / v_new
+  void *k_cache;
+  void *v_cache;
+  const float *freqs_cis;
+  const int32_t *kv_len_dev; // tokens already cached per sequence, or NULL
+  const int32_t *rope_pos_dev;
+  int kv_len;           // used when kv_len_dev == NULL
+  int m;                // query tokens per sequence; m * group <= 16
+  int offset;           // causal: row r sees positions < min(total, offset + r + 1); <0 disables
+  int append;           // 1: rotate + append the new token (m == 1)
+  int rotate_q;
+  int is_neox;
+  int chunk;            // positions per split (multiple of 64)
+  int max_splits;       // grid.x
+  float *ws_o;          // [rows][max_splits][128] fp32, rows = batch*m*H
+  float *ws_lse;        // [rows][max_splits] (log2 domain)
+  float scale_log2;
+};
+
+cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t stream, int *launches);
+
+// merge of split results held in (ws_o, ws_lse); also used for cross-device parts
+struct MergeParams {
+  void *out;               // dtype, element (row, d) at row_off(row) + d; may be NULL
+  float *o_partial;        // fp32 [rows][128] or NULL
+  float *lse_partial;      // natural log
+  const float *parts_o;    // [rows][max_parts][128] (part_major == 0) or [parts][rows][128]
+  const float *parts_lse;
+  int part_major;
+  int lse_is_log2;         // workspace partials are in the log2 domain
+  int rows, max_parts;
+  // number of valid parts per row: fixed n_parts, or ceil(total_b / chunk)
+  int n_parts;
+  const int32_t *kv_len_dev;
+  int kv_len, append, chunk;
+  int rows_per_seq;        // m * H
+  int n_heads, m;
+  long out_seq, out_tok;   // output strides
+};
+
+cudaError_t launch_attn_merge(const MergeParams &p, bool bf16, cudaStream_t stream);
+
+// ---- general causal attention (mma.sync, any m/n/offset) -----------------------
+struct PrefillParams {
+  AttnGeom g;
+  void *out;
+  const void *q; // rotated
+  const void *k_cache;
+  const void *v_cache;
+  int m, n, offset;
+  float scale_log2;
+};
+
+cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStream_t stream);
+
+// tcgen05 / TMEM / TMA kernel; same contract.  Returns cudaErrorNotSupported if
+// the geometry cannot be described by its tensor maps.
+cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream);
+
+} // namespace b200attn

@@ -1,0 +1,199 @@
+"""ctypes binding of libgpu_ops.so: one Python function per C entry point of
+include/gpu_ops.h, same names, same argument order.
+
+Tensor arguments are torch CUDA tensors (or raw integer device addresses); the
+wrappers pass ``data_ptr()`` through and launch on torch's current stream unless
+``stream`` is given.  A non-zero status raises GpuOpsError with the library's
+message.  Nothing here computes anything: without the compiled library every
+call fails.
+"""
+import ctypes
+import os
+
+DT_FLOAT16 = 4   # reference DataType values (prebuild/defs.hpp:8-18)
+DT_BFLOAT16 = 5
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgpu_ops.so")
+_lib = None
+
+EXPORTS = [
+    "gpu_flash_attn_layer", "gpu_flash_attn_gqa_layer", "gpu_flash_attn_opt_prefill_layer",
+    "gpu_rope_layer", "gpu_rope_single_layer", "gpu_rope_kv_append_layer", "gpu_attn_prefill_layer",
+    "gpu_attn_decode_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer",
+    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
+    "gpu_ops_launch_count", "gpu_ops_last_error_string",
+]
+
+
+class GpuOpsError(RuntimeError):
+    pass
+
+
+class AttnDesc(ctypes.Structure):
+    """struct gpu_attn_desc (include/gpu_ops.h); strides in elements."""
+    _fields_ = [
+        ("dtype", ctypes.c_int32), ("batch", ctypes.c_int32), ("n_heads", ctypes.c_int32),
+        ("n_kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("is_neox_style", ctypes.c_int32),
+        ("q_seq_stride", ctypes.c_int64), ("q_tok_stride", ctypes.c_int64),
+        ("kv_in_seq_stride", ctypes.c_int64), ("kv_in_tok_stride", ctypes.c_int64),
+        ("out_seq_stride", ctypes.c_int64), ("out_tok_stride", ctypes.c_int64),
+        ("cache_seq_stride", ctypes.c_int64), ("cache_head_stride", ctypes.c_int64),
+        ("cache_pos_stride", ctypes.c_int64),
+    ]
+
+
+def make_desc(dtype, batch, n_heads, n_kv_heads, m, max_pos, layout="head", is_neox=False, head_dim=128):
+    """Descriptor for dense q/out [batch][m][H][D], raw k/v [batch][m][kvH][D] and a
+    cache of `max_pos` positions per sequence: head-major [batch][kvH][max_pos][D]
+    or token-major [batch][max_pos][kvH][D] (the reference's layout)."""
+    d = AttnDesc()
+    d.dtype, d.batch, d.n_heads, d.n_kv_heads, d.head_dim = dtype, batch, n_heads, n_kv_heads, head_dim
+    d.is_neox_style = int(bool(is_neox))
+    d.q_tok_stride = n_heads * head_dim
+    d.q_seq_stride = m * d.q_tok_stride
+    d.out_tok_stride = n_heads * head_dim
+    d.out_seq_stride = m * d.out_tok_stride
+    d.kv_in_tok_stride = n_kv_heads * head_dim
+    d.kv_in_seq_stride = m * d.kv_in_tok_stride
+    d.cache_seq_stride = n_kv_heads * max_pos * head_dim
+    if layout == "head":
+        d.cache_head_stride, d.cache_pos_stride = max_pos * head_dim, head_dim
+    elif layout == "token":
+        d.cache_head_stride, d.cache_pos_stride = head_dim, n_kv_heads * head_dim
+    else:
+        raise ValueError(layout)
+    return d
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "%s is missing: build it with `python -m llm_simple_b200.build` "
+                "(there is no CPU or PyTorch fallback)" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        vp, i, i32p, f32p = ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p
+        dp = ctypes.POINTER(AttnDesc)
+        L.gpu_flash_attn_layer.argtypes = [vp] * 4 + [i] * 6 + [vp]
+        L.gpu_flash_attn_opt_prefill_layer.argtypes = [vp] * 4 + [i] * 6 + [vp]
+        L.gpu_flash_attn_gqa_layer.argtypes = [vp] * 4 + [i] * 7 + [vp]
+        L.gpu_rope_layer.argtypes = [vp] * 5 + [i] * 6 + [vp]
+        L.gpu_rope_single_layer.argtypes = [vp] * 3 + [i] * 6 + [vp]
+        L.gpu_rope_kv_append_layer.argtypes = [dp] + [vp] * 7 + [i32p, i, i, vp]
+        L.gpu_attn_prefill_layer.argtypes = [dp] + [vp] * 4 + [i, i, vp]
+        L.gpu_attn_decode_layer.argtypes = [dp, vp, f32p, f32p] + [vp] * 6 + [i32p, i32p, i, i, vp,
+                                                                               ctypes.c_size_t, vp]
+        L.gpu_attn_decode_workspace_bytes.argtypes = [dp, i]
+        L.gpu_attn_decode_workspace_bytes.restype = ctypes.c_size_t
+        L.gpu_attn_merge_lse_layer.argtypes = [vp, f32p, f32p, i, i, i, i, vp]
+        L.gpu_ops_set_workspace.argtypes = [vp, ctypes.c_size_t]
+        L.gpu_attn_set_decode_chunk.argtypes = [i]
+        L.gpu_attn_set_prefill_kernel.argtypes = [i]
+        L.gpu_ops_launch_count.argtypes = [i]
+        L.gpu_ops_launch_count.restype = ctypes.c_long
+        L.gpu_ops_last_error_string.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is not None:
+        return stream if isinstance(stream, int) else stream.cuda_stream
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc):
+    if rc != 0:
+        raise GpuOpsError("gpu_ops status %d: %s" % (rc, lib().gpu_ops_last_error_string().decode()))
+
+
+def last_error_string():
+    return lib().gpu_ops_last_error_string().decode()
+
+
+def gpu_flash_attn_layer(output, q, k, v, m, n, offset, head_num, head_dim, dt, stream=None):
+    _check(lib().gpu_flash_attn_layer(_ptr(output), _ptr(q), _ptr(k), _ptr(v), m, n, offset, head_num,
+                                      head_dim, dt, _stream(stream)))
+
+
+def gpu_flash_attn_opt_prefill_layer(output, q, k, v, m, n, offset, head_num, head_dim, dt, stream=None):
+    _check(lib().gpu_flash_attn_opt_prefill_layer(_ptr(output), _ptr(q), _ptr(k), _ptr(v), m, n, offset,
+                                                  head_num, head_dim, dt, _stream(stream)))
+
+
+def gpu_flash_attn_gqa_layer(output, q, k, v, m, n, offset, group_size, kv_head_num, head_dim, dt,
+                             stream=None):
+    _check(lib().gpu_flash_attn_gqa_layer(_ptr(output), _ptr(q), _ptr(k), _ptr(v), m, n, offset, group_size,
+                                          kv_head_num, head_dim, dt, _stream(stream)))
+
+
+def gpu_rope_layer(output_q, output_k, freqs_cis, input_q, input_k, start_pos, cur_size, n_heads,
+                   hidden_dim, is_neox_style, dt, stream=None):
+    _check(lib().gpu_rope_layer(_ptr(output_q), _ptr(output_k), _ptr(freqs_cis), _ptr(input_q),
+                                _ptr(input_k), start_pos, cur_size, n_heads, hidden_dim,
+                                int(bool(is_neox_style)), dt, _stream(stream)))
+
+
+def gpu_rope_single_layer(output_x, freqs_cis, input_x, start_pos, cur_size, n_heads, hidden_dim,
+                          is_neox_style, dt, stream=None):
+    _check(lib().gpu_rope_single_layer(_ptr(output_x), _ptr(freqs_cis), _ptr(input_x), start_pos, cur_size,
+                                       n_heads, hidden_dim, int(bool(is_neox_style)), dt, _stream(stream)))
+
+
+def gpu_rope_kv_append_layer(desc, q_out, k_cache, v_cache, q_in, k_in, v_in, freqs_cis, start_pos_dev,
+                             start_pos, m, stream=None):
+    _check(lib().gpu_rope_kv_append_layer(ctypes.byref(desc), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                          _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(freqs_cis),
+                                          _ptr(start_pos_dev), start_pos, m, _stream(stream)))
+
+
+def gpu_attn_prefill_layer(desc, out, q, k_cache, v_cache, m, offset, stream=None):
+    _check(lib().gpu_attn_prefill_layer(ctypes.byref(desc), _ptr(out), _ptr(q), _ptr(k_cache),
+                                        _ptr(v_cache), m, offset, _stream(stream)))
+
+
+def gpu_attn_decode_workspace_bytes(desc, max_kv_len):
+    return int(lib().gpu_attn_decode_workspace_bytes(ctypes.byref(desc), max_kv_len))
+
+
+def gpu_attn_decode_layer(desc, out, o_partial, lse_partial, q_in, k_in, v_in, k_cache, v_cache, freqs_cis,
+                          kv_len_dev, rope_pos_dev, append_new, max_kv_len, workspace, workspace_bytes,
+                          stream=None):
+    _check(lib().gpu_attn_decode_layer(ctypes.byref(desc), _ptr(out), _ptr(o_partial), _ptr(lse_partial),
+                                       _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(k_cache), _ptr(v_cache),
+                                       _ptr(freqs_cis), _ptr(kv_len_dev), _ptr(rope_pos_dev),
+                                       int(bool(append_new)), max_kv_len, _ptr(workspace), workspace_bytes,
+                                       _stream(stream)))
+
+
+def gpu_attn_merge_lse_layer(out, o_parts, lse_parts, n_parts, rows, head_dim, dt, stream=None):
+    _check(lib().gpu_attn_merge_lse_layer(_ptr(out), _ptr(o_parts), _ptr(lse_parts), n_parts, rows,
+                                          head_dim, dt, _stream(stream)))
+
+
+def gpu_ops_set_workspace(workspace, nbytes):
+    _check(lib().gpu_ops_set_workspace(_ptr(workspace), nbytes))
+
+
+def gpu_attn_set_decode_chunk(positions):
+    _check(lib().gpu_attn_set_decode_chunk(positions))
+
+
+def gpu_attn_set_prefill_kernel(which):
+    _check(lib().gpu_attn_set_prefill_kernel(which))
+
+
+def gpu_ops_launch_count(reset=False):
+    return int(lib().gpu_ops_launch_count(int(bool(reset))))

@@ -1,0 +1,51 @@
+"""CPU checks of the drop-in boundary: the library loads and exports every
+symbol the public header declares; nothing is computed (no GPU here)."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "gpu_ops.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gpu_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from llm_simple_b200 import ops
+    lib = ctypes.CDLL(ops.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(ops.EXPORTS) == names
+
+
+def test_descriptor_struct_matches_the_header_layout():
+    from llm_simple_b200 import ops
+    # 6 x int32 then 9 x int64, no padding
+    assert ctypes.sizeof(ops.AttnDesc) == 6 * 4 + 9 * 8
+    assert ops.AttnDesc.q_seq_stride.offset == 24
+    d = ops.make_desc(ops.DT_BFLOAT16, 2, 40, 8, 1, 4096, layout="head")
+    assert (d.cache_head_stride, d.cache_pos_stride, d.cache_seq_stride) == (4096 * 128, 128, 8 * 4096 * 128)
+    t = ops.make_desc(ops.DT_FLOAT16, 1, 32, 32, 256, 256, layout="token")
+    assert (t.cache_head_stride, t.cache_pos_stride) == (128, 32 * 128)
+
+
+def test_data_type_values_are_the_reference_ones():
+    text = open(os.path.join(ROOT, "include", "defs.hpp")).read()
+    body = re.search(r"enum DataType[^{]*\{(.*?)\}", text, flags=re.S).group(1)
+    names = [x.strip().split("=")[0].strip() for x in body.split(",") if x.strip()]
+    assert names.index("DT_FLOAT16") == 4 and names.index("DT_BFLOAT16") == 5 and names.index("DT_FLOAT32") == 6
+
+
+def test_host_side_validation_needs_no_gpu():
+    from llm_simple_b200 import ops
+    L = ops.lib()
+    assert L.gpu_attn_set_decode_chunk(100) != 0
+    assert b"multiple of 64" in L.gpu_ops_last_error_string()
+    assert L.gpu_attn_set_decode_chunk(0) == 0
+    assert L.gpu_flash_attn_layer(None, None, None, None, 4, 4, 0, 2, 64, 4, None) == -2
+    assert L.gpu_attn_decode_workspace_bytes(None, 10) == 0
