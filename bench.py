@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload ("cfg4"): one decode step of a Qwen2.5-14B-shaped model's
+attention -- 48 layers, batch 64, 40 query heads on 8 KV heads, head_dim 128,
+bf16, per-sequence cache lengths uniform in [1024, 4096] from a seed, RoPE theta
+1e6 -- with the KV heads sharded over the N GPUs (no collective on the data
+path).  One step = for every layer one fused launch group: rotate the new
+token's Q/K, append K/V to the cache, split-KV grouped-query attention, merge.
+The metric is algorithmic HBM GB/s (every K/V byte once + q/k/v in + o out), the
+sum over all ranks divided by the slowest rank's device time.
+
+Also reported in the same JSON line: the prefill leg ("cfg3": Llama-2-13B-shaped
+causal prefill, batch 8 x 2048 tokens, 40 heads, fp16; algorithmic TFLOP/s), the
+end-to-end figure with host buffers, the roofline of the dominant kernel, and the
+CPU restatement of the reference's layer timed on the host cores.
+
+Synthetic seeded N(0,1) tensors stand in for real activations (no checkpoints
+here).  `--impl reference` times only the CPU restatement of the reference path
+(the reference's own CPU layer needs Eigen/boost/spdlog, which are not
+installed, so it cannot be built).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+D = 128
+DT_FP16, DT_BF16 = 4, 5
+
+CFG4 = dict(name="cfg4 Qwen2.5-14B-shaped batched GQA decode", layers=48, batch=64, n_heads=40, n_kv_heads=8,
+            len_lo=1024, len_hi=4096, theta=1e6, neox=True, seed=20254)
+CFG3 = dict(name="cfg3 Llama-2-13B-shaped causal prefill", batch=8, seq=2048, n_heads=40, theta=1e4, neox=False)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tensor=p["bf16_tflops"], tensor_sustained=p.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+def decode_bytes(lens_with_new, n_heads, n_kv_heads):
+    """Algorithmic bytes of one layer's decode step: K and V once, q in, o out,
+    raw k/v in, rotated k and v appended."""
+    eb = 2
+    per_seq = [2 * n_kv_heads * L * D * eb + 2 * n_heads * D * eb + 4 * n_kv_heads * D * eb for L in lens_with_new]
+    return float(sum(per_seq))
+
+
+def prefill_flops(batch, heads, m, offset):
+    """4*D per unmasked (row, col) pair."""
+    pairs = m * offset + m * (m + 1) // 2
+    return 4.0 * D * heads * batch * pairs
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for i, n in enumerate(names):
+                if len(r) > 3 + i and r[3 + i].lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------
+# CPU restatement of the reference layer, timed (cpu_baseline / --impl reference)
+# ----------------------------------------------------------------------------
+def cpu_decode_layer(orc, cfg, lens, threads, rng):
+    """One layer of the decode step on the host, the way the reference's layer
+    runs it: rope(q), rope(k) -> append -> attention, strict rounding points,
+    sequence by sequence.  Returns seconds."""
+    H, kvh = cfg["n_heads"], cfg["n_kv_heads"]
+    dt = orc.DT_BFLOAT16
+    max_pos = max(lens) + 1
+    table = orc.init_freq_cis(D, max_pos, cfg["theta"], dt)
+    caches = []
+    for L in lens:
+        caches.append((orc.to_bits(rng.standard_normal((L + 1, kvh * D), dtype=np.float32), dt),
+                       orc.to_bits(rng.standard_normal((L + 1, kvh * D), dtype=np.float32), dt)))
+    q = orc.to_bits(rng.standard_normal((len(lens), H * D), dtype=np.float32), dt)
+    k = orc.to_bits(rng.standard_normal((len(lens), kvh * D), dtype=np.float32), dt)
+    v = orc.to_bits(rng.standard_normal((len(lens), kvh * D), dtype=np.float32), dt)
+    t0 = time.perf_counter()
+    for b, L in enumerate(lens):
+        kc, vc = caches[b]
+        q_r = orc.rope_single_layer(q[b:b + 1], table, L, H, cfg["neox"], dt)
+        k_r = orc.rope_single_layer(k[b:b + 1], table, L, kvh, cfg["neox"], dt)
+        orc.kv_append(kc, vc, k_r, v[b:b + 1], L, kvh, D)
+        orc.attn(q_r, kc, vc, 1, L + 1, L, H // kvh, kvh, D, dt, orc.MODE_STRICT, threads=threads)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(cfg, lens, budget_s=12.0, seqs=None):
+    from oracle import oracle as orc
+    threads = orc.max_threads()
+    rng = np.random.default_rng(7)
+    sample = list(lens if seqs is None else lens[:seqs])
+    nbytes = decode_bytes([L + 1 for L in sample], cfg["n_heads"], cfg["n_kv_heads"])
+    times = []
+    t_start = time.perf_counter()
+    while not times or (time.perf_counter() - t_start < budget_s and len(times) < 5):
+        times.append(cpu_decode_layer(orc, cfg, sample, threads, rng))
+    best = min(times)
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "1 layer x %d of %d sequences, %d repeats, best; strict rounding points, OpenMP over KV heads"
+                      % (len(sample), len(lens), len(times)),
+            "seconds": best}
+
+
+def run_reference_arm(args, cfg, lens):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    threads = orc.max_threads()
+    rng = np.random.default_rng(7)
+    seqs = 16  # bounded sample of the batch per step
+    sample = lens[:seqs]
+    nbytes = decode_bytes([L + 1 for L in sample], cfg["n_heads"], cfg["n_kv_heads"])
+    for _ in range(args.warmup):
+        cpu_decode_layer(orc, cfg, sample, threads, rng)
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_decode_layer(orc, cfg, sample, threads, rng)
+    value = nbytes * args.steps / t / 1e9
+    line = {
+        "impl": "reference", "metric": "attn decode HBM GB/s per layer", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg["name"], "note": "CPU restatement of the reference layer on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "each step = 1 layer x %d of %d sequences" % (seqs, len(lens))},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling on a small case)")
+    ap.add_argument("--batch", type=int, default=None, help="override the batch (profiling on a small case)")
+    ap.add_argument("--no-extras", action="store_true", help="skip prefill leg, e2e and CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    cfg = dict(CFG4)
+    if args.layers:
+        cfg["layers"] = args.layers
+    if args.batch:
+        cfg["batch"] = args.batch
+    rng = np.random.default_rng(cfg["seed"])
+    lens = [int(x) for x in rng.integers(cfg["len_lo"], cfg["len_hi"] + 1, size=cfg["batch"])]
+
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, lens)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from llm_simple_b200 import ops
+    from oracle import oracle as orc  # table builder + cpu_baseline leg only
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ops.lib()
+    pk = peaks()
+
+    H, kvh = cfg["n_heads"], cfg["n_kv_heads"]
+    if kvh % world:
+        raise SystemExit("KV heads (%d) do not divide over %d ranks" % (kvh, world))
+    kvh_l, H_l = kvh // world, H // world
+    layers, batch = cfg["layers"], cfg["batch"]
+    max_pos = cfg["len_hi"] + 8
+    max_kv = max(lens) + 1
+    dev = torch.device("cuda", local_rank)
+
+    # ---- device state: per-layer head-major caches [batch][kvh_l][max_pos][D], seeded N(0,1)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(cfg["seed"] + rank)
+    k_cache = [torch.empty((batch, kvh_l, max_pos, D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+               for _ in range(layers)]
+    v_cache = [torch.empty((batch, kvh_l, max_pos, D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+               for _ in range(layers)]
+    q_in = torch.empty((layers, batch, H_l * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    k_in = torch.empty((layers, batch, kvh_l * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    v_in = torch.empty((layers, batch, kvh_l * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    out = torch.empty((layers, batch, H_l * D), dtype=torch.bfloat16, device=dev)
+    table = torch.from_numpy(orc.init_freq_cis(D, max_pos, cfg["theta"], orc.DT_BFLOAT16)).to(dev)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=dev)
+    desc = ops.make_desc(DT_BF16, batch, H_l, kvh_l, 1, max_pos, layout="head", is_neox=cfg["neox"])
+    ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, max_kv)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for l in range(layers):
+            ops.gpu_attn_decode_layer(desc, out[l], None, None, q_in[l], k_in[l], v_in[l], k_cache[l], v_cache[l],
+                                      table, lens_d, None, True, max_kv, ws, ws_bytes, stream=stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops.gpu_ops_launch_count(True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        barrier()
+    launches = ops.gpu_ops_launch_count(True)
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        lt = torch.tensor([launches], dtype=torch.int64, device=dev)
+        dist.all_reduce(lt)
+        launches = int(lt.item())
+    ms_per_step = ms / args.steps
+    bytes_layer_all = decode_bytes([L + 1 for L in lens], H, kvh)         # all ranks, one layer
+    bytes_layer_rank = decode_bytes([L + 1 for L in lens], H_l, kvh_l)    # this rank, one layer
+    value = bytes_layer_all * layers / (ms_per_step * 1e-3) / 1e9
+    layer_ms = ms_per_step / layers
+    achieved = bytes_layer_rank / (layer_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": achieved / pk["hbm"], "traffic": None, "peak_source": pk["source"],
+                "kernel": "attn_decode_kernel (+ attn_merge_kernel, one launch pair per layer)",
+                "launch_ms": layer_ms, "algorithmic_bytes_per_launch": bytes_layer_rank,
+                "frac_of_nominal_8TBs": achieved / 8000.0}
+
+    line = {
+        "metric": "attn decode HBM GB/s per layer", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg["name"], "layers": layers, "batch": batch, "n_heads": H, "n_kv_heads": kvh,
+                   "head_dim": D, "kv_len": "uniform[%d,%d] seed %d" % (cfg["len_lo"], cfg["len_hi"], cfg["seed"]),
+                   "sharding": "kv-head x%d" % world, "cache_layout": "head-major",
+                   "l2": "inputs larger than L2 (%.0f MB per layer, %.1f GB per step per rank)"
+                         % (bytes_layer_rank / 1e6, bytes_layer_rank * layers / 1e9)},
+        "roofline": roofline, "clocks": clk.summary(), "gpu_launches": launches,
+    }
+
+    if not args.no_extras:
+        line["e2e"] = e2e_leg(torch, ops, args, cfg, desc, lens, lens_d, k_cache, v_cache, table, ws, ws_bytes,
+                              max_kv, H_l, kvh_l, world, dev, barrier, bytes_layer_all)
+        line["prefill"] = prefill_leg(torch, ops, orc, world, dev, barrier, pk)
+        if rank == 0 and world == 1:
+            line["cpu_baseline"] = cpu_baseline(cfg, lens)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def e2e_leg(torch, ops, args, cfg, desc, lens, lens_d, k_cache, v_cache, table, ws, ws_bytes, max_kv, H_l, kvh_l,
+            world, dev, barrier, bytes_layer_all):
+    """The same step with HOST buffers: every layer's q/k/v of the new token come
+    from pinned host memory and its attention output goes back to pinned host
+    memory, copies inside the timed region.  The KV cache is device state."""
+    import torch.distributed as dist
+    layers, batch = cfg["layers"], cfg["batch"]
+    qkv_w = (H_l + 2 * kvh_l) * D
+    h_in = torch.empty((layers, batch, qkv_w), dtype=torch.bfloat16).normal_().pin_memory()
+    h_out = torch.empty((layers, batch, H_l * D), dtype=torch.bfloat16).pin_memory()
+    d_in = torch.empty((2, batch, qkv_w), dtype=torch.bfloat16, device=dev)
+    d_out = torch.empty((2, batch, H_l * D), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream()
+    # the fused op reads q, k, v out of one [batch][(H+2kvH)*D] row: strides in the descriptor
+    d2 = ops.AttnDesc.from_buffer_copy(desc)
+    d2.q_seq_stride = qkv_w
+    d2.kv_in_seq_stride = qkv_w
+
+    def step():
+        for l in range(layers):
+            s = l & 1
+            d_in[s].copy_(h_in[l], non_blocking=True)
+            base = d_in[s].data_ptr()
+            ops.gpu_attn_decode_layer(d2, d_out[s], None, None, base, base + H_l * D * 2,
+                                      base + (H_l + kvh_l) * D * 2, k_cache[l], v_cache[l], table, lens_d, None,
+                                      True, max_kv, ws, ws_bytes, stream=stream)
+            h_out[l].copy_(d_out[s], non_blocking=True)
+
+    steps = max(3, args.steps // 2)
+    for _ in range(3):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record(stream)
+    for _ in range(steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    ms = max(ev0.elapsed_time(ev1), 0.0)
+    if world > 1:
+        t = torch.tensor([ms, wall_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, wall_ms = float(t[0].item()), float(t[1].item())
+    per_step = ms / steps
+    return {"value": bytes_layer_all * layers / (per_step * 1e-3) / 1e9, "unit": "GB/s",
+            "h2d_bytes_per_step": int(layers * batch * qkv_w * 2 * world),
+            "d2h_bytes_per_step": int(layers * batch * H_l * D * 2 * world), "ms_per_step": per_step,
+            "wall_ms_per_step": wall_ms / steps, "steps": steps,
+            "api": "gpu_attn_decode_layer per layer, pinned host q/k/v in and attention output back"}
+
+
+def prefill_leg(torch, ops, orc, world, dev, barrier, pk):
+    """cfg3 prefill, one layer pass: fused RoPE + KV append, then causal attention."""
+    import torch.distributed as dist
+    c = CFG3
+    if c["n_heads"] % world:
+        return {"skipped": "heads do not divide"}
+    H_l = c["n_heads"] // world
+    batch, S = c["batch"], c["seq"]
+    max_pos = S + 256
+    desc = ops.make_desc(DT_FP16, batch, H_l, H_l, S, max_pos, layout="head", is_neox=c["neox"])
+    q = torch.randn((batch, S, H_l * D), dtype=torch.float16, device=dev)
+    k = torch.randn_like(q)
+    v = torch.randn_like(q)
+    qe = torch.empty_like(q)
+    o = torch.empty_like(q)
+    kc = torch.zeros((batch, H_l, max_pos, D), dtype=torch.float16, device=dev)
+    vc = torch.zeros_like(kc)
+    table = torch.from_numpy(orc.init_freq_cis(D, max_pos, c["theta"], orc.DT_FLOAT16)).to(dev)
+    stream = torch.cuda.current_stream()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+
+    def layer_pass(attn_only=False):
+        if not attn_only:
+            ops.gpu_rope_kv_append_layer(desc, qe, kc, vc, q, k, v, table, None, 0, S, stream=stream)
+        ops.gpu_attn_prefill_layer(desc, o, qe, kc, vc, S, 0, stream=stream)
+
+    res = {}
+    for name, attn_only in (("layer_pass", False), ("attention_only", True)):
+        for _ in range(3):
+            layer_pass(attn_only)
+        times = []
+        for _ in range(10):
+            flush.zero_()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            layer_pass(attn_only)
+            e1.record(stream)
+            barrier()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            times.append(ms)
+        ms = statistics.median(times)
+        fl = prefill_flops(batch, c["n_heads"], S, 0)
+        res[name] = {"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12, "ms_min": min(times)}
+    per_rank = res["attention_only"]["tflops"] / world
+    res.update({"workload": c["name"], "dtype": "fp16", "flops_per_layer": prefill_flops(batch, c["n_heads"], S, 0),
+                "l2": "256 MB flush between iterations",
+                "roofline": {"bound": "tensor", "achieved": per_rank, "peak": pk["tensor"], "unit": "TFLOP/s",
+                             "frac": per_rank / pk["tensor"], "peak_source": pk["source"],
+                             "frac_of_nominal_2250": per_rank / 2250.0, "kernel": "prefill attention kernel"}})
+    return res
+
+
+if __name__ == "__main__":
+    main()
