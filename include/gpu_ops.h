@@ -161,6 +161,32 @@ int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial
                           const int32_t *rope_pos_dev, int append_new, int max_kv_len,
                           void *workspace, size_t workspace_bytes, gpu_stream_t stream);
 
+/* The same fused decode step for callers that may not allocate device memory
+ * (no counterpart in the reference: its operators leave allocation to the
+ * caller's pool, src/device_npu.cpp:22-67).  Some hosts cannot call cudaMalloc
+ * when a decode step runs: a serving process that reserved all of the GPU's
+ * memory for its own KV-cache pool at start-up, a plug-in slot that must not
+ * allocate after initialisation, a latency-critical loop that cannot afford
+ * cudaMalloc's device-wide synchronisation.  They have no way to supply
+ * gpu_attn_decode_layer's workspace.  This entry point
+ * needs none: its split-KV scratch is a fixed 16 MiB array in the library's own
+ * device image, held by every GPU that loads the library until the process
+ * exits.  It calls no cudaMalloc / cudaFree and no allocating routine.
+ *   - Splits are always 512 positions; a call needs batch * n_heads *
+ *     ceil(max_kv_len / 512) * 516 bytes of scratch and is rejected with
+ *     GPU_OPS_E_WORKSPACE (nothing launched) when that exceeds 16 MiB.
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current); make that first call before any stream capture.
+ *   - All calls on a device share the array, which keeps the previous call's
+ *     contents; nothing in it needs clearing, but calls whose kernels overlap on
+ *     the GPU race on it: order them on one stream or with events.
+ * Arguments as gpu_attn_decode_layer, without the partial outputs and workspace. */
+int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const void *q_in,
+                                  const void *k_in, const void *v_in, void *k_cache,
+                                  void *v_cache, const void *freqs_cis_dev,
+                                  const int32_t *kv_len_dev, const int32_t *rope_pos_dev,
+                                  int append_new, int max_kv_len, gpu_stream_t stream);
+
 /* Scratch bytes gpu_attn_decode_layer needs for this geometry and bound. */
 size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len);
 

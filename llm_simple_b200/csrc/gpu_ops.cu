@@ -235,6 +235,10 @@ int ref_rope(void *out_q, void *out_k, const void *freqs, const void *in_q, cons
 
 } // namespace
 
+namespace b200attn {
+void set_last_error(const char *msg) { g_last_error = msg ? msg : ""; }
+} // namespace b200attn
+
 extern "C" {
 
 int gpu_flash_attn_layer(void *output_dev, const void *q_dev, const void *k_dev, const void *v_dev, int m, int n,

@@ -7,6 +7,9 @@
 
 namespace b200attn {
 
+// Record the message gpu_ops_last_error_string() returns on the calling thread.
+void set_last_error(const char *msg);
+
 // ---- RoPE + append ---------------------------------------------------------
 // One of up to three tensors handled by a rope_append launch (Q, K, V).
 struct RopeStream {

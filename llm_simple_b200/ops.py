@@ -20,7 +20,7 @@ _lib = None
 EXPORTS = [
     "gpu_flash_attn_layer", "gpu_flash_attn_gqa_layer", "gpu_flash_attn_opt_prefill_layer",
     "gpu_rope_layer", "gpu_rope_single_layer", "gpu_rope_kv_append_layer", "gpu_attn_prefill_layer",
-    "gpu_attn_decode_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer",
+    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string",
 ]
@@ -86,6 +86,7 @@ def lib():
         L.gpu_attn_prefill_layer.argtypes = [dp] + [vp] * 4 + [i, i, vp]
         L.gpu_attn_decode_layer.argtypes = [dp, vp, f32p, f32p] + [vp] * 6 + [i32p, i32p, i, i, vp,
                                                                                ctypes.c_size_t, vp]
+        L.gpu_attn_decode_layer_noalloc.argtypes = [dp] + [vp] * 7 + [i32p, i32p, i, i, vp]
         L.gpu_attn_decode_workspace_bytes.argtypes = [dp, i]
         L.gpu_attn_decode_workspace_bytes.restype = ctypes.c_size_t
         L.gpu_attn_merge_lse_layer.argtypes = [vp, f32p, f32p, i, i, i, i, vp]
@@ -176,6 +177,17 @@ def gpu_attn_decode_layer(desc, out, o_partial, lse_partial, q_in, k_in, v_in, k
                                        _ptr(freqs_cis), _ptr(kv_len_dev), _ptr(rope_pos_dev),
                                        int(bool(append_new)), max_kv_len, _ptr(workspace), workspace_bytes,
                                        _stream(stream)))
+
+
+def gpu_attn_decode_layer_noalloc(desc, out, q_in, k_in, v_in, k_cache, v_cache, freqs_cis, kv_len_dev,
+                                  rope_pos_dev, append_new, max_kv_len, stream=None):
+    """The fused decode step with the library's built-in 16 MiB scratch: for callers
+    that cannot allocate device memory.  Make the first call on a device outside any
+    stream capture; do not overlap calls on one device."""
+    _check(lib().gpu_attn_decode_layer_noalloc(ctypes.byref(desc), _ptr(out), _ptr(q_in), _ptr(k_in),
+                                               _ptr(v_in), _ptr(k_cache), _ptr(v_cache), _ptr(freqs_cis),
+                                               _ptr(kv_len_dev), _ptr(rope_pos_dev), int(bool(append_new)),
+                                               max_kv_len, _stream(stream)))
 
 
 def gpu_attn_merge_lse_layer(out, o_parts, lse_parts, n_parts, rows, head_dim, dt, stream=None):
