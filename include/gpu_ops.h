@@ -215,6 +215,12 @@ int gpu_attn_set_decode_chunk(int positions);
  * 2 = tcgen05 kernel.  Process-wide; for tests and measurements. */
 int gpu_attn_set_prefill_kernel(int which);
 
+/* 0, or the code of the first wait inside a kernel on the current device that
+ * gave up: every device-side wait (mbarrier polls of the tcgen05 kernel) is
+ * bounded to about a second, after which the kernel records a code here, ends
+ * normally and leaves the context usable.  Read it after synchronising. */
+int gpu_ops_kernel_status(void);
+
 /* Number of kernels launched by this library on the calling thread since the
  * last call with reset != 0. */
 long gpu_ops_launch_count(int reset);

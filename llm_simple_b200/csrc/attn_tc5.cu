@@ -1,5 +1,493 @@
-// placeholder until the tcgen05 kernel lands
+// Causal prefill attention on the 5th-generation tensor cores (sm_100a):
+// tcgen05.mma with accumulators in tensor memory (TMEM), operands staged in
+// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), online softmax
+// in registers.
+//
+// One CTA = 128 query rows of one head of one sequence, walking the KV cache in
+// tiles of 128 positions up to the causal diagonal.
+//   warp 0        TMA producer (one elected lane): Q once, then K and V tiles
+//                 into two-stage rings
+//   warp 1        MMA issuer (one elected lane): S = Q.K^T (operands from shared
+//                 memory) into one of two TMEM buffers, then O += P.V with P
+//                 read from TMEM and V from shared memory (N-major operand)
+//   warps 2-5     softmax, one thread per query row (TMEM lane): tcgen05.ld of
+//                 the S row, running max / sum in the log2 domain, P written
+//                 back over S as packed 16-bit pairs (tcgen05.st); O is only
+//                 rescaled when the running max has grown by more than 2^8
+//                 since the last rescale; epilogue O / l -> global memory
+// S for tile j+1 is computed while the softmax of tile j runs.
+//
+// Reference semantics: tests/flash_attn_test.cpp:106-192 (mask col > row+offset,
+// scale 1/sqrt(D) folded into the exponent, O = softmax(S).V, out [m][H*D]).
+//
+// Every wait on an mbarrier is bounded: after about a second without progress
+// the waiter raises an error flag that the host reads, and the CTA runs to its
+// normal end (TMEM is freed) instead of spinning.
 #include "kernels.h"
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <type_traits>
+
 namespace b200attn {
-cudaError_t launch_attn_prefill_tc5(const PrefillParams &, bool, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace tc5 {
+
+constexpr int kBM = 128;            // query rows per CTA
+constexpr int kBN = 128;            // key positions per tile
+constexpr int kThreads = 192;
+constexpr int kStages = 2;
+constexpr uint32_t kHalfTile = 128 * 128;        // bytes of a [128 rows][64 elem] swizzled half tile
+constexpr uint32_t kTileBytes = 2 * kHalfTile;   // [128][128] 16-bit
+constexpr uint32_t kSmemQ = 0;
+constexpr uint32_t kSmemK = kSmemQ + kTileBytes;
+constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
+constexpr uint32_t kSmemBar = kSmemV + kStages * kTileBytes;
+constexpr uint32_t kSmemTotal = kSmemBar + 256 + 1024; // barriers + slack for 1024-byte alignment
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+constexpr float kRescaleThreshold = 8.0f;        // log2 domain
+
+// barrier slots (8 bytes each) inside the barrier block
+enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
+       BAR_ODONE = 13, BAR_COUNT = 14 };
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Bounded wait.  Returns false (and raises the flags) when the phase has not
+// completed within ~2e9 cycles, or at once when another waiter already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          int *error_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 2000000000LL) {
+        *abort_flag = 1;
+        *reinterpret_cast<volatile int *>(error_flag) = code;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t *r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+//   K-major operand  ([rows][64 elem] half tiles): LBO field 1 (unused), SBO = 1024 B (8 rows)
+//   MN-major operand (V: [pos][64 elem] half tiles): LBO = distance between the two 64-element
+//   halves, SBO = 1024 B (8 positions)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3fff);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= static_cast<uint64_t>(1) << 46;  // descriptor version (Blackwell)
+  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, A/B format fmt (0 fp16, 1 bf16), M = 128, N = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (b_mn_major << 16) | ((128u >> 3) << 17) |
+         ((128u >> 4) << 24);
+}
+
+struct Params {
+  void *out;
+  int m, n, offset;
+  int group;
+  long out_seq, out_tok;
+  float scale_log2;
+  int *error_flag;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kSmemBar;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + BAR_COUNT * 8);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / p.group;
+  const int row0 = qt * kBM;
+  const int row_end = min(p.m, row0 + kBM);
+  const int kv_end = min(p.n, p.offset + row_end);
+  const int ntiles = (kv_end + kBN - 1) / kBN;
+  constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  constexpr uint32_t idesc_qk = instr_desc(fmt, 0), idesc_pv = instr_desc(fmt, 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(BAR_Q), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(BAR_KFULL + s), 1);
+      mbar_init(bar(BAR_KEMPTY + s), 1);
+      mbar_init(bar(BAR_VFULL + s), 1);
+      mbar_init(bar(BAR_VEMPTY + s), 1);
+      mbar_init(bar(BAR_SFULL + s), 1);
+      mbar_init(bar(BAR_PREADY + s), 128);
+    }
+    mbar_init(bar(BAR_ODONE), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(const_cast<uint32_t *>(tmem_slot))),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(bar(BAR_Q), kTileBytes);
+      tma_load_4d(smem_base + kSmemQ, &map_q, bar(BAR_Q), 0, h, row0, b);
+      tma_load_4d(smem_base + kSmemQ + kHalfTile, &map_q, bar(BAR_Q), 64, h, row0, b);
+      for (int j = 0; j < ntiles; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) break;
+        mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
+        tma_load_4d(smem_base + kSmemK + s * kTileBytes, &map_k, bar(BAR_KFULL + s), 0, j * kBN, kvh, b);
+        tma_load_4d(smem_base + kSmemK + s * kTileBytes + kHalfTile, &map_k, bar(BAR_KFULL + s), 64, j * kBN, kvh, b);
+        if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2)) break;
+        mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
+        tma_load_4d(smem_base + kSmemV + s * kTileBytes, &map_v, bar(BAR_VFULL + s), 0, j * kBN, kvh, b);
+        tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, &map_v, bar(BAR_VFULL + s), 64, j * kBN, kvh, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_flag, 3);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % kStages;
+        if (!mbar_wait(bar(BAR_KFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 4)) return false;
+        tc_fence_after();
+        const uint32_t d = tmem + ((j & 1) ? kColS1 : kColS0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t koff = (k >> 2) * kHalfTile + (k & 3) * 32;
+          tc_mma_ss(d, smem_desc(smem_base + kSmemQ + koff, 16, 1024),
+                    smem_desc(smem_base + kSmemK + s * kTileBytes + koff, 16, 1024), idesc_qk, k > 0);
+        }
+        tc_commit(bar(BAR_KEMPTY + s));
+        tc_commit(bar(BAR_SFULL + (j & 1)));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      if (ok && ntiles > 1) ok = issue_qk(1);
+      for (int j = 0; ok && j < ntiles; ++j) {
+        const int s = j % kStages;
+        if (!mbar_wait(bar(BAR_PREADY + (j & 1)), (j >> 1) & 1, abort_flag, p.error_flag, 5)) break;
+        if (!mbar_wait(bar(BAR_VFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 6)) break;
+        tc_fence_after();
+        const uint32_t pcol = tmem + ((j & 1) ? kColS1 : kColS0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // 16 positions per step: 8 TMEM columns of packed P, 16 rows (2048 B) of V
+          tc_mma_ts(tmem + kColO, pcol + 8 * k, smem_desc(smem_base + kSmemV + s * kTileBytes + k * 2048, kHalfTile, 1024),
+                    idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(BAR_VEMPTY + s));
+        tc_commit(bar(BAR_ODONE));
+        if (j + 2 < ntiles) ok = issue_qk(j + 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue
+    const int quad = warp & 3;                   // TMEM lane quadrant this warp may touch
+    const int row_in_tile = quad * 32 + lane;
+    const int row = row0 + row_in_tile;          // query token index within the call
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int vis_end = min(p.n, p.offset + row + 1); // columns < vis_end are visible to this row
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + (j & 1)), (j >> 1) & 1, abort_flag, p.error_flag, 7))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t scol = tmem + lane_addr + ((j & 1) ? kColS1 : kColS0);
+      uint32_t su[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld32(scol + 32 * c, su + 32 * c);
+      tc_wait_ld();
+      const int col0 = j * kBN;
+      // only the last tiles of a row block cross the diagonal or the end of the cache
+      if (col0 + kBN > min(p.n, p.offset + row0 + 1)) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (col0 + c >= vis_end) su[c] = 0xff800000u; // -inf
+      }
+      float mx = __uint_as_float(su[0]);
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(su[c]));
+      mx *= p.scale_log2;
+      // lazy rescale: keep the old reference max unless the new one is much larger
+      const bool grow = mx > m_ref + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow) && j > 0) {
+        // O must hold every P.V issued so far before it is rescaled
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE), (j - 1) & 1, abort_flag, p.error_flag, 8))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float f = grow ? ex2(m_ref - mx) : 1.f;
+        l *= f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tc_ld32(tmem + lane_addr + kColO + 32 * c, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tc_st32(tmem + lane_addr + kColO + 32 * c, o);
+        }
+        tc_wait_st();
+      }
+      if (grow) m_ref = mx;
+      uint32_t pk[64];
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = ex2(fmaf(__uint_as_float(su[2 * c]), p.scale_log2, -m_ref));
+        const float p1 = ex2(fmaf(__uint_as_float(su[2 * c + 1]), p.scale_log2, -m_ref));
+        sum += p0 + p1;
+        pk[c] = Elem<T>::pack(p0, p1);
+      }
+      l += sum;
+      tc_st32(scol, pk);
+      tc_st32(scol + 32, pk + 32);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_PREADY + (j & 1)));
+    }
+    if (ok && ntiles > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE), (ntiles - 1) & 1, abort_flag, p.error_flag, 9));
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T *dst = static_cast<T *>(p.out) + b * p.out_seq + static_cast<long>(row) * p.out_tok + h * kHeadDim;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tc_ld32(tmem + lane_addr + kColO + 32 * c, o);
+        tc_wait_ld();
+        if (row < p.m) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 u;
+            u.x = Elem<T>::pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            u.y = Elem<T>::pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            u.z = Elem<T>::pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            u.w = Elem<T>::pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4 *>(dst + 32 * c + i) = u;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 4-D map over (d, dim1, dim2, dim3) with a box of 64 x box1 x box2 x 1 elements
+bool make_map(CUtensorMap *map, bool bf16, const void *base, uint64_t n1, uint64_t n2, uint64_t n3, long s1, long s2,
+              long s3, uint32_t box1, uint32_t box2) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  auto fix = [](long s) { return static_cast<cuuint64_t>(s > 0 ? s : 128) * 2; }; // bytes; unit extents may carry stride 0
+  cuuint64_t dims[4] = {128, n1, n2, n3};
+  cuuint64_t strides[3] = {fix(s1), fix(s2), fix(s3)};
+  cuuint32_t box[4] = {64, box1, box2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16 || strides[i] >= (1ull << 40)) return false;
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// device word the kernels raise when a bounded wait gives up; one per device
+int *error_word() {
+  static std::mutex mu;
+  static int *words[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!words[dev]) {
+    // mapped pinned host memory: the kernel writes it, the host reads it without a copy
+    int *h = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void **>(&h), sizeof(int), cudaHostAllocMapped) != cudaSuccess) return nullptr;
+    *h = 0;
+    words[dev] = h;
+  }
+  return words[dev];
+}
+
+} // namespace tc5
+
+int attn_tc5_error_status() {
+  int *w = tc5::error_word();
+  return w ? *reinterpret_cast<volatile int *>(w) : 0;
+}
+
+cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream) {
+  using namespace tc5;
+  const AttnGeom &g = p.g;
+  CUtensorMap mq, mk, mv;
+  // q: (d, head, token, seq); k/v: (d, pos, kv_head, seq)
+  if (!make_map(&mq, bf16, p.q, g.n_heads, p.m, g.batch, kHeadDim, g.q_tok, g.q_seq, 1, kBM) ||
+      !make_map(&mk, bf16, p.k_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1) ||
+      !make_map(&mv, bf16, p.v_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1))
+    return cudaErrorNotSupported;
+  int *err = error_word();
+  if (!err) return cudaErrorNotSupported;
+  int *err_dev = nullptr;
+  if (cudaHostGetDevicePointer(reinterpret_cast<void **>(&err_dev), err, 0) != cudaSuccess) return cudaErrorNotSupported;
+  Params kp{};
+  kp.out = p.out;
+  kp.m = p.m;
+  kp.n = p.n;
+  kp.offset = p.offset;
+  kp.group = g.group;
+  kp.out_seq = g.out_seq;
+  kp.out_tok = g.out_tok;
+  kp.scale_log2 = p.scale_log2;
+  kp.error_flag = err_dev;
+  dim3 grid((p.m + kBM - 1) / kBM, g.n_heads, g.batch);
+  cudaError_t e;
+  if (bf16) {
+    e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return e;
+    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, kp);
+  } else {
+    e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return e;
+    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, kp);
+  }
+  return cudaGetLastError();
+}
+
+} // namespace b200attn

@@ -455,6 +455,8 @@ int gpu_attn_set_prefill_kernel(int which) {
   return GPU_OPS_OK;
 }
 
+int gpu_ops_kernel_status(void) { return attn_tc5_error_status(); }
+
 long gpu_ops_launch_count(int reset) {
   const long n = g_launches;
   if (reset) g_launches = 0;

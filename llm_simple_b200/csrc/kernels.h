@@ -108,5 +108,7 @@ cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStrea
 // tcgen05 / TMEM / TMA kernel; same contract.  Returns cudaErrorNotSupported if
 // the geometry cannot be described by its tensor maps.
 cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream);
+// Non-zero once a bounded wait inside a tcgen05 kernel on the current device has given up.
+int attn_tc5_error_status();
 
 } // namespace b200attn

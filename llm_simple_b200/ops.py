@@ -22,7 +22,7 @@ EXPORTS = [
     "gpu_rope_layer", "gpu_rope_single_layer", "gpu_rope_kv_append_layer", "gpu_attn_prefill_layer",
     "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
-    "gpu_ops_launch_count", "gpu_ops_last_error_string",
+    "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
 ]
 
 
@@ -205,6 +205,10 @@ def gpu_attn_set_decode_chunk(positions):
 
 def gpu_attn_set_prefill_kernel(which):
     _check(lib().gpu_attn_set_prefill_kernel(which))
+
+
+def gpu_ops_kernel_status():
+    return int(lib().gpu_ops_kernel_status())
 
 
 def gpu_ops_launch_count(reset=False):

@@ -30,6 +30,8 @@ def prefill_kernel(request, ops):
     ops.gpu_attn_set_prefill_kernel(request.param)
     yield request.param
     ops.gpu_attn_set_prefill_kernel(0)
+    # no device-side wait gave up (every wait in the tcgen05 kernel is bounded and reports here)
+    assert ops.gpu_ops_kernel_status() == 0
 
 
 def run_gqa(ops, q, k, v, m, n, offset, g, kvh, dt):
