@@ -6,6 +6,6 @@ ctypes wrappers (``llm_simple_b200.ops``) that take torch tensors for device
 memory and streams.  There is no CPU or PyTorch fallback: a missing library is
 an ImportError at first use.
 """
-from . import ops  # noqa: F401
+from . import layer, ops  # noqa: F401
 
-__all__ = ["ops"]
+__all__ = ["ops", "layer"]

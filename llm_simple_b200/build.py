@@ -17,10 +17,10 @@ OBJ = os.path.join(HERE, "csrc", "_obj")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CUDA_SOURCES = ["rope_append.cu", "attn_mma.cu", "attn_tc5.cu", "gpu_ops.cu", "decode_noalloc.cu"]
-CXX_SOURCES = []
+CXX_SOURCES = ["host/device_gpu.cpp", "host/attention_layer_gpu.cpp", "host/host_abi.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"),
-          "-I", CSRC, "-ccbin", "g++"]
+          "-I", CSRC, "-I", os.path.join(CSRC, "host"), "-ccbin", "g++"]
 
 
 def _newer(src_paths, target):
@@ -32,7 +32,7 @@ def _newer(src_paths, target):
 
 def _deps():
     out = []
-    for d in (CSRC, os.path.join(ROOT, "include")):
+    for d in (CSRC, os.path.join(CSRC, "host"), os.path.join(ROOT, "include")):
         for f in os.listdir(d):
             if f.endswith((".h", ".hpp", ".cuh")):
                 out.append(os.path.join(d, f))
@@ -46,7 +46,7 @@ def build(force=False, verbose=False):
     procs = []
     for src in CUDA_SOURCES + CXX_SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
+        o = os.path.join(OBJ, os.path.splitext(src)[0].replace("/", "_") + ".o")
         objs.append(o)
         if force or _newer([s] + deps, o):
             cmd = [NVCC] + ARCH + COMMON + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]

@@ -1,0 +1,270 @@
+#include "attention_layer_gpu.hpp"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+// ---- RoPE table (src/model_base.cpp:27-66, src/util.cpp:33-72) -------------------
+static uint16_t fp32_to_bfloat16_rne(uint32_t bits) {
+  const uint32_t sign = (bits >> 31) & 1u, exponent = (bits >> 23) & 0xffu;
+  const uint32_t sig = (bits & 0x007fffffu) | 0x00800000u;
+  uint32_t hi = (sig >> 16) & 0xffu;
+  const uint32_t lo = sig & 0xffffu;
+  if (lo > 0x8000u || (lo == 0x8000u && (hi & 1u))) hi += 1;
+  uint32_t e = exponent;
+  if (hi > 0xffu) {
+    e += 1;
+    hi = 0x80u;
+  }
+  if (e > 0xffu) e = 0xffu;
+  return static_cast<uint16_t>((sign << 15) | (e << 7) | (hi & 0x7fu));
+}
+
+void InitFreqCIS(float *out, int head_dim, int max_seq_len, float theta, DataType dt) {
+  const int freq_len = head_dim / 2;
+  std::vector<float> freq(freq_len);
+  for (int i = 0; i < freq_len; ++i)
+    freq[i] = 1.0f / (std::pow(theta, static_cast<double>(i * 2) / static_cast<double>(head_dim)));
+  for (int pos = 0; pos < max_seq_len; ++pos) {
+    const float t = static_cast<float>(pos);
+    for (int j = 0; j < freq_len; ++j) {
+      const float angle = t * freq[j];
+      float c = std::cos(angle), s = std::sin(angle);
+      if (dt == DT_BFLOAT16) {
+        uint32_t u;
+        std::memcpy(&u, &c, 4);
+        u = static_cast<uint32_t>(fp32_to_bfloat16_rne(u)) << 16;
+        std::memcpy(&c, &u, 4);
+        std::memcpy(&u, &s, 4);
+        u = static_cast<uint32_t>(fp32_to_bfloat16_rne(u)) << 16;
+        std::memcpy(&s, &u, 4);
+      }
+      out[(static_cast<size_t>(pos) * freq_len + j) * 2] = c;
+      out[(static_cast<size_t>(pos) * freq_len + j) * 2 + 1] = s;
+    }
+  }
+}
+
+// ---- layer -----------------------------------------------------------------------
+AttentionLayerGPUImpl::~AttentionLayerGPUImpl() { UnInit(); }
+
+void AttentionLayerGPUImpl::UnInit() {
+  k_cache.reset();
+  v_cache.reset();
+  freq_cis_owned_.reset();
+  workspace_.reset();
+  kv_len_dev_.reset();
+  staging_in_.reset();
+  staging_out_.reset();
+  if (kv_len_pinned_) {
+    cudaFreeHost(kv_len_pinned_);
+    kv_len_pinned_ = nullptr;
+  }
+  k_cache_raw_ = v_cache_raw_ = nullptr;
+  freq_cis_ = nullptr;
+}
+
+bool AttentionLayerGPUImpl::Init(const AttentionConfig &cfg, const float *shared_freq_cis, void *k_cache_ext,
+                                 void *v_cache_ext) {
+  UnInit();
+  if (cfg.n_heads <= 0 || cfg.n_kv_heads <= 0 || cfg.n_heads % cfg.n_kv_heads || cfg.head_dim != 128 ||
+      cfg.max_seq_len <= 0 || cfg.max_batch <= 0 || (cfg.data_type != DT_FLOAT16 && cfg.data_type != DT_BFLOAT16) ||
+      (k_cache_ext == nullptr) != (v_cache_ext == nullptr)) {
+    std::fprintf(stderr, "AttentionLayerGPUImpl::Init: invalid configuration\n");
+    return false;
+  }
+  cfg_ = cfg;
+  // cache: reference allocates kvH * D * max_seq_len 16-bit elements per layer
+  // (src/llama2_layer_npu.cpp:726-727, :1148-1149); here once per sequence of the batch
+  const size_t cache_elems = static_cast<size_t>(cfg.max_batch) * cfg.n_kv_heads * cfg.max_seq_len * cfg.head_dim;
+  if (k_cache_ext) {
+    k_cache_raw_ = k_cache_ext;
+    v_cache_raw_ = v_cache_ext;
+  } else {
+    k_cache = Tensor::MakeGPUTensor(cache_elems, cfg.data_type);
+    v_cache = Tensor::MakeGPUTensor(cache_elems, cfg.data_type);
+    if (!k_cache->data_ptr || !v_cache->data_ptr) return false;
+    k_cache_raw_ = k_cache->data_ptr;
+    v_cache_raw_ = v_cache->data_ptr;
+  }
+  if (shared_freq_cis) {
+    freq_cis_ = shared_freq_cis;
+  } else {
+    const size_t n = static_cast<size_t>(cfg.max_seq_len) * cfg.head_dim;
+    auto host = Tensor::MakeCPUTensor(n, DT_FLOAT32);
+    InitFreqCIS(static_cast<float *>(host->data_ptr), cfg.head_dim, cfg.max_seq_len, cfg.rope_theta, cfg.data_type);
+    freq_cis_owned_ = host->to(DEV_GPU);
+    if (!freq_cis_owned_ || !freq_cis_owned_->data_ptr) return false;
+    freq_cis_ = static_cast<const float *>(freq_cis_owned_->data_ptr);
+  }
+  gpu_attn_desc d = MakeDesc(cfg.max_batch, 1, 0, 0, 0, 0);
+  workspace_bytes_ = gpu_attn_decode_workspace_bytes(&d, cfg.max_seq_len);
+  workspace_ = Tensor::MakeGPUTensor(workspace_bytes_ > 0 ? workspace_bytes_ : 16, DT_UINT8);
+  kv_len_dev_ = Tensor::MakeGPUTensor(cfg.max_batch, DT_INT32);
+  if (cudaHostAlloc(reinterpret_cast<void **>(&kv_len_pinned_), sizeof(int32_t) * cfg.max_batch, cudaHostAllocDefault) !=
+      cudaSuccess)
+    return false;
+  return workspace_->data_ptr && kv_len_dev_->data_ptr;
+}
+
+gpu_attn_desc AttentionLayerGPUImpl::MakeDesc(int batch, int m, long q_tok, long q_seq, long kv_tok, long kv_seq) const {
+  gpu_attn_desc d{};
+  const long D = cfg_.head_dim;
+  d.dtype = static_cast<int32_t>(cfg_.data_type);
+  d.batch = batch;
+  d.n_heads = cfg_.n_heads;
+  d.n_kv_heads = cfg_.n_kv_heads;
+  d.head_dim = cfg_.head_dim;
+  d.is_neox_style = cfg_.rope_is_neox_style ? 1 : 0;
+  d.q_tok_stride = q_tok ? q_tok : cfg_.n_heads * D;
+  d.q_seq_stride = q_seq ? q_seq : m * d.q_tok_stride;
+  d.kv_in_tok_stride = kv_tok ? kv_tok : cfg_.n_kv_heads * D;
+  d.kv_in_seq_stride = kv_seq ? kv_seq : m * d.kv_in_tok_stride;
+  d.out_tok_stride = cfg_.n_heads * D;
+  d.out_seq_stride = m * d.out_tok_stride;
+  d.cache_seq_stride = static_cast<long>(cfg_.n_kv_heads) * cfg_.max_seq_len * D;
+  if (cfg_.cache_layout == CacheLayout::HeadMajor) {
+    d.cache_head_stride = static_cast<long>(cfg_.max_seq_len) * D;
+    d.cache_pos_stride = D;
+  } else {
+    d.cache_head_stride = D;
+    d.cache_pos_stride = cfg_.n_kv_heads * D;
+  }
+  return d;
+}
+
+int AttentionLayerGPUImpl::UploadLens(const int32_t *lens, int batch, cudaStream_t stream) {
+  // the pinned staging array is reused by every call: wait until the previous upload has been read
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return GPU_OPS_E_CUDA;
+  std::memcpy(kv_len_pinned_, lens, sizeof(int32_t) * batch);
+  e = cudaMemcpyAsync(kv_len_dev_->data_ptr, kv_len_pinned_, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, stream);
+  return e == cudaSuccess ? GPU_OPS_OK : GPU_OPS_E_CUDA;
+}
+
+int AttentionLayerGPUImpl::ForwardRaw(void *out, const void *q, const void *k, const void *v, InferenceCtx &ctx,
+                                      int batch) {
+  if (batch <= 0 || batch > cfg_.max_batch || ctx.cur_size <= 0 || ctx.prev_pos < 0 || ctx.cur_pos > cfg_.max_seq_len)
+    return GPU_OPS_E_INVALID;
+  cudaStream_t s = ctx.gpu_stream;
+  if (ctx.cur_size == 1) {
+    // decode: every sequence sits at prev_pos
+    std::vector<int32_t> lens(batch, ctx.prev_pos);
+    return DecodeRagged(out, q, k, v, lens.data(), batch, s);
+  }
+  gpu_attn_desc d = MakeDesc(batch, ctx.cur_size, 0, 0, 0, 0);
+  // rotate Q in a pooled temporary (the reference's q_emb), K/V straight into the cache
+  auto q_emb = Tensor::MakeGPUTensor(static_cast<size_t>(batch) * ctx.cur_size * cfg_.n_heads * cfg_.head_dim,
+                                     cfg_.data_type);
+  if (!q_emb->data_ptr) return GPU_OPS_E_CUDA;
+  int rc = gpu_rope_kv_append_layer(&d, q_emb->data_ptr, k_cache_raw_, v_cache_raw_, q, k, v, freq_cis_, nullptr,
+                                    ctx.prev_pos, ctx.cur_size, s);
+  if (rc) return rc;
+  rc = gpu_attn_prefill_layer(&d, out, q_emb->data_ptr, k_cache_raw_, v_cache_raw_, ctx.cur_size, ctx.prev_pos, s);
+  // q_emb returns to the pool when it goes out of scope; the pool is not
+  // stream-aware, and later users of the block are ordered after this kernel
+  // because the layer issues everything on the same stream.
+  return rc;
+}
+
+int AttentionLayerGPUImpl::DecodeRagged(void *out, const void *q, const void *k, const void *v,
+                                        const int32_t *kv_len_host, int batch, cudaStream_t stream) {
+  if (batch <= 0 || batch > cfg_.max_batch) return GPU_OPS_E_INVALID;
+  if (shared_lens_) {
+    gpu_attn_desc d = MakeDesc(batch, 1, 0, 0, 0, 0);
+    return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_, shared_lens_,
+                                 nullptr, 1, shared_max_len_, workspace_->data_ptr, workspace_bytes_, stream);
+  }
+  if (!kv_len_host) return GPU_OPS_E_INVALID;
+  int max_len = 0;
+  for (int b = 0; b < batch; ++b) {
+    if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
+    if (kv_len_host[b] + 1 > max_len) max_len = kv_len_host[b] + 1;
+  }
+  int rc = UploadLens(kv_len_host, batch, stream);
+  if (rc) return rc;
+  gpu_attn_desc d = MakeDesc(batch, 1, 0, 0, 0, 0);
+  return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_,
+                               static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
+                               workspace_->data_ptr, workspace_bytes_, stream);
+}
+
+std::shared_ptr<Tensor> AttentionLayerGPUImpl::Forward(std::shared_ptr<Tensor> q, std::shared_ptr<Tensor> k,
+                                                       std::shared_ptr<Tensor> v, InferenceCtx &ctx, int batch) {
+  auto out = Tensor::MakeGPUTensor(static_cast<size_t>(batch) * ctx.cur_size * cfg_.n_heads * cfg_.head_dim,
+                                   cfg_.data_type);
+  if (!out->data_ptr) return nullptr;
+  if (ForwardRaw(out->data_ptr, q->data_ptr, k->data_ptr, v->data_ptr, ctx, batch) != GPU_OPS_OK) return nullptr;
+  return out;
+}
+
+int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, InferenceCtx &ctx, int batch,
+                                       const int32_t *kv_len_host) {
+  if (batch <= 0 || batch > cfg_.max_batch || ctx.cur_size <= 0) return GPU_OPS_E_INVALID;
+  const long D = cfg_.head_dim;
+  const long row = (cfg_.n_heads + 2L * cfg_.n_kv_heads) * D;
+  const size_t in_bytes = static_cast<size_t>(batch) * ctx.cur_size * row * 2;
+  const size_t out_bytes = static_cast<size_t>(batch) * ctx.cur_size * cfg_.n_heads * D * 2;
+  if (in_bytes > staging_in_bytes_) {
+    staging_in_ = Tensor::MakeGPUTensor(in_bytes, DT_UINT8);
+    staging_in_bytes_ = in_bytes;
+  }
+  if (out_bytes > staging_out_bytes_) {
+    staging_out_ = Tensor::MakeGPUTensor(out_bytes, DT_UINT8);
+    staging_out_bytes_ = out_bytes;
+  }
+  cudaStream_t s = ctx.gpu_stream;
+  if (cudaMemcpyAsync(staging_in_->data_ptr, qkv_host, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return GPU_OPS_E_CUDA;
+  const char *base = static_cast<const char *>(staging_in_->data_ptr);
+  const void *q = base, *k = base + cfg_.n_heads * D * 2, *v = base + (cfg_.n_heads + cfg_.n_kv_heads) * D * 2;
+  int rc;
+  if (ctx.cur_size == 1 && shared_lens_) {
+    gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
+    rc = gpu_attn_decode_layer(&d, staging_out_->data_ptr, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_,
+                               freq_cis_, shared_lens_, nullptr, 1, shared_max_len_, workspace_->data_ptr,
+                               workspace_bytes_, s);
+  } else if (ctx.cur_size == 1) {
+    std::vector<int32_t> uniform;
+    if (!kv_len_host) {
+      uniform.assign(batch, ctx.prev_pos);
+      kv_len_host = uniform.data();
+    }
+    int max_len = 0;
+    for (int b = 0; b < batch; ++b) {
+      if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
+      if (kv_len_host[b] + 1 > max_len) max_len = kv_len_host[b] + 1;
+    }
+    if ((rc = UploadLens(kv_len_host, batch, s))) return rc;
+    // q, k, v are columns of one packed row: strides say so
+    gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
+    rc = gpu_attn_decode_layer(&d, staging_out_->data_ptr, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_,
+                               freq_cis_, static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
+                               workspace_->data_ptr, workspace_bytes_, s);
+  } else {
+    gpu_attn_desc d = MakeDesc(batch, ctx.cur_size, row, ctx.cur_size * row, row, ctx.cur_size * row);
+    // rotate Q in place inside the staging buffer
+    rc = gpu_rope_kv_append_layer(&d, const_cast<void *>(q), k_cache_raw_, v_cache_raw_, q, k, v, freq_cis_, nullptr,
+                                  ctx.prev_pos, ctx.cur_size, s);
+    if (!rc)
+      rc = gpu_attn_prefill_layer(&d, staging_out_->data_ptr, q, k_cache_raw_, v_cache_raw_, ctx.cur_size,
+                                  ctx.prev_pos, s);
+  }
+  if (rc) return rc;
+  if (cudaMemcpyAsync(out_host, staging_out_->data_ptr, out_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return GPU_OPS_E_CUDA;
+  return GPU_OPS_OK;
+}
+
+bool Llamma2AttentionGPUImpl::Init(const AttentionConfig &cfg, const float *shared_freq_cis, void *k_cache_ext,
+                                   void *v_cache_ext) {
+  AttentionConfig c = cfg;
+  c.n_kv_heads = c.n_heads;     // MHA: the cache holds n_heads * head_dim per position
+  c.data_type = DT_FLOAT16;     // src/llama2_main.cpp:172
+  return AttentionLayerGPUImpl::Init(c, shared_freq_cis, k_cache_ext, v_cache_ext);
+}
+
+bool Qwen2AttentionGPUImpl::Init(const AttentionConfig &cfg, const float *shared_freq_cis, void *k_cache_ext,
+                                 void *v_cache_ext) {
+  return AttentionLayerGPUImpl::Init(cfg, shared_freq_cis, k_cache_ext, v_cache_ext);
+}

@@ -1,0 +1,134 @@
+// The attention section of the transformer layers on the GPU backend.
+//
+// Mirrors what Llamma2TransformerLayerNPUImpl / Qwen2TransformerLayerNPUImpl
+// (src/llama2_layer_npu.hpp:43-95) hold and do between the Q/K/V projections and
+// o_proj (src/llama2_layer_npu.cpp:283-374, :780-869): members k_cache / v_cache,
+// the RoPE table, and a Forward that rotates, appends and attends.  Everything
+// else of those layers (norms, GEMMs, MLP) is outside this library.
+//
+// Added relative to the reference, which is batch 1: a batch dimension
+// (independent sequences with their own cache rows) and ragged decode lengths.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <vector>
+
+#include "device.hpp"
+#include "gpu_ops.h"
+
+// Same fields as the reference's InferenceCtx (src/model_base.hpp:40-48); the
+// stream is a CUDA stream.
+class InferenceCtx {
+public:
+  InferenceCtx(size_t cur_pos, size_t prev_pos) : cur_pos(int(cur_pos)), prev_pos(int(prev_pos)) {
+    cur_size = this->cur_pos - this->prev_pos; // src/model_base.cpp:22-25
+  }
+  int cur_pos;
+  int prev_pos;
+  int cur_size;
+  cudaStream_t gpu_stream{nullptr};
+};
+
+// Host builder of the RoPE table, ModelBase::InitFreqCIS (src/model_base.cpp:27-66):
+// freq[i] = 1 / pow(theta, 2i / D) in double rounded to float, angle = float(pos) * freq[i]
+// in fp32, (cos, sin) interleaved; for DT_BFLOAT16 every value is rounded to bf16
+// (ties to even, src/util.cpp:33-72) and stored back as fp32.
+// out: [max_seq_len][head_dim/2][2].
+void InitFreqCIS(float *out, int head_dim, int max_seq_len, float theta, DataType dt);
+
+enum class CacheLayout { TokenMajor = 0, HeadMajor = 1 };
+
+struct AttentionConfig {
+  int n_heads{0};
+  int n_kv_heads{0};
+  int head_dim{128};
+  int max_seq_len{2048};
+  int max_batch{1};
+  DataType data_type{DT_FLOAT16};
+  float rope_theta{10000.0f};
+  bool rope_is_neox_style{false};
+  CacheLayout cache_layout{CacheLayout::HeadMajor};
+};
+
+class AttentionLayerGPUImpl {
+public:
+  virtual ~AttentionLayerGPUImpl();
+
+  // Allocates the caches ([max_batch] x layout of [max_seq_len][n_kv_heads][D]),
+  // the decode scratch and the RoPE table (or adopts `shared_freq_cis`, a device
+  // table built once per model as the reference does).  External cache memory
+  // may be adopted instead of allocated (both or neither).
+  virtual bool Init(const AttentionConfig &cfg, const float *shared_freq_cis = nullptr, void *k_cache_ext = nullptr,
+                    void *v_cache_ext = nullptr);
+  virtual void UnInit();
+
+  // Attention section for `batch` sequences that all sit at ctx.prev_pos and
+  // receive ctx.cur_size new tokens: q [batch][cur_size][n_heads*D],
+  // k, v [batch][cur_size][n_kv_heads*D] raw projections (device).  Returns the
+  // [batch][cur_size][n_heads*D] tensor that feeds o_proj.
+  std::shared_ptr<Tensor> Forward(std::shared_ptr<Tensor> q, std::shared_ptr<Tensor> k, std::shared_ptr<Tensor> v,
+                                  InferenceCtx &ctx, int batch = 1);
+
+  // Same on raw device pointers, output preallocated by the caller.
+  int ForwardRaw(void *out, const void *q, const void *k, const void *v, InferenceCtx &ctx, int batch);
+
+  // One decode step with per-sequence cache lengths (host array, `batch` entries).
+  int DecodeRagged(void *out, const void *q, const void *k, const void *v, const int32_t *kv_len_host, int batch,
+                   cudaStream_t stream);
+
+  // Host-buffer entry: q/k/v packed as [batch][cur_size][(n_heads + 2 n_kv_heads)*D]
+  // in (pinned) host memory, output to host memory; copies are enqueued on the
+  // stream around the kernels.  kv_len_host == NULL: uniform ctx.prev_pos.
+  int ForwardHost(void *out_host, const void *qkv_host, InferenceCtx &ctx, int batch, const int32_t *kv_len_host);
+
+  // Per-step state shared by all layers of a model: the device array of cache
+  // lengths (tokens already cached per sequence) and its maximum + 1.  While
+  // set, decode calls use it instead of uploading their own copy (one upload per
+  // step by the model instead of one per layer).  NULL unsets.
+  void SetSharedLens(const int32_t *kv_len_dev, int max_kv_len) {
+    shared_lens_ = kv_len_dev;
+    shared_max_len_ = max_kv_len;
+  }
+
+  const AttentionConfig &config() const { return cfg_; }
+  void *k_cache_ptr() const { return k_cache_raw_; }
+  void *v_cache_ptr() const { return v_cache_raw_; }
+
+  std::shared_ptr<Tensor> k_cache; // owned caches (empty when external memory was adopted)
+  std::shared_ptr<Tensor> v_cache;
+
+protected:
+  gpu_attn_desc MakeDesc(int batch, int m, long q_tok, long q_seq, long kv_tok, long kv_seq) const;
+  int UploadLens(const int32_t *lens, int batch, cudaStream_t stream);
+
+  AttentionConfig cfg_;
+  void *k_cache_raw_{nullptr};
+  void *v_cache_raw_{nullptr};
+  std::shared_ptr<Tensor> freq_cis_owned_;
+  const float *freq_cis_{nullptr};
+  std::shared_ptr<Tensor> workspace_;
+  size_t workspace_bytes_{0};
+  std::shared_ptr<Tensor> kv_len_dev_;
+  int32_t *kv_len_pinned_{nullptr};
+  std::shared_ptr<Tensor> staging_in_, staging_out_; // device side of ForwardHost
+  size_t staging_in_bytes_{0}, staging_out_bytes_{0};
+  const int32_t *shared_lens_{nullptr};
+  int shared_max_len_{0};
+};
+
+// Llama-2 flavour: MHA, fp16 (the reference forces DT_FLOAT16 for llama2,
+// src/llama2_main.cpp:172), RoPE pairing from the flag.
+class Llamma2AttentionGPUImpl : public AttentionLayerGPUImpl {
+public:
+  bool Init(const AttentionConfig &cfg, const float *shared_freq_cis = nullptr, void *k_cache_ext = nullptr,
+            void *v_cache_ext = nullptr) override;
+};
+
+// Qwen2 flavour: GQA, bf16 or fp16.
+class Qwen2AttentionGPUImpl : public AttentionLayerGPUImpl {
+public:
+  bool Init(const AttentionConfig &cfg, const float *shared_freq_cis = nullptr, void *k_cache_ext = nullptr,
+            void *v_cache_ext = nullptr) override;
+};

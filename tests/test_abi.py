@@ -7,8 +7,8 @@ import re
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "gpu_ops.h")).read()
+def declared_symbols(header="gpu_ops.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(gpu_[a-z0-9_]+)\s*\(", text)))
 
@@ -21,6 +21,15 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
     assert sorted(ops.EXPORTS) == names
+
+
+def test_library_exports_every_symbol_of_the_host_layer_header():
+    from llm_simple_b200 import layer, ops
+    lib = ctypes.CDLL(ops.LIB_PATH)
+    names = declared_symbols("gpu_layer.h")
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(layer.EXPORTS) == names
 
 
 def test_descriptor_struct_matches_the_header_layout():

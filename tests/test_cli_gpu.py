@@ -1,0 +1,48 @@
+"""Runs the C++ operator test programs (tests/cli), the counterparts of the
+reference's op_test_flash_attn and op_test_rope_single command-line tests, with
+the reference's flags.  They exercise the C++ host layer (Tensor, GPUAllocator)
+and the C ABI from C++ and compare with the CPU checker."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+CLI = os.path.join(HERE, "cli")
+
+
+@pytest.fixture(scope="module")
+def binaries():
+    env = dict(os.environ)
+    env.pop("CXX", None)
+    subprocess.check_call(["make", "-C", CLI], env=env, stdout=subprocess.DEVNULL)
+    return os.path.join(CLI, "bin")
+
+
+def run(binary, *args):
+    r = subprocess.run([binary] + [str(a) for a in args], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "test success" in r.stdout
+    return r.stdout
+
+
+@pytest.mark.parametrize("args", [
+    ("--m", 256, "--n", 256, "--offset", 0, "--head_num", 32, "--head_dim", 128),   # Llama-2-7B-shaped prefill
+    ("--m", 1, "--n", 700, "--offset", 699, "--head_num", 32),                       # decode shape
+    ("--m", 300, "--n", 812, "--offset", 512, "--head_num", 4, "--mode", "strict"),
+    ("--m", 200, "--n", 200, "--group_size", 5, "--kv_head_num", 2, "--dtype", "bfloat16"),
+])
+def test_flash_attn_main(binaries, args):
+    out = run(os.path.join(binaries, "flash_attn_main"), *args)
+    assert "within(1e-2,1e-3)" in out
+
+
+@pytest.mark.parametrize("args", [
+    ("--dtype", "float16"),                                                           # reference defaults
+    ("--dtype", "bfloat16", "--seq_len", 77, "--offset", 4000, "--head_num", 12),
+    ("--dtype", "float16", "--is_neox", "false", "--seq_len", 1, "--offset", 5, "--head_num", 40),
+])
+def test_rope_single_layer_main(binaries, args):
+    out = run(os.path.join(binaries, "rope_single_layer_main"), *args)
+    assert "bit-identical: yes" in out
