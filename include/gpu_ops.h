@@ -198,6 +198,15 @@ int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_p
                              int n_parts, int rows, int head_dim, int dt,
                              gpu_stream_t stream);
 
+/* The same merge on the receive buffer of an all-gather: part p (one per rank)
+ * is one contiguous block of rows*(head_dim+1) floats, first the rows*head_dim
+ * normalised outputs, then the rows log-sum-exps -- what a rank gets when it
+ * points gpu_attn_decode_layer's o_partial at its send buffer and lse_partial
+ * at send buffer + rows*head_dim.  The partial (O, LSE) exchange has no
+ * counterpart in the reference, which is single-device. */
+int gpu_attn_merge_packed_layer(void *out, const float *parts, int n_parts, int rows, int head_dim,
+                                int dt, gpu_stream_t stream);
+
 /* Scratch for the reference-shaped attention operators on the CURRENT device.
  * They take no workspace argument (the reference's signatures have none) and
  * never allocate; with scratch registered, decode-shaped calls (m * group_size

@@ -241,17 +241,22 @@ template <typename T> __global__ void __launch_bounds__(128) attn_merge_kernel(M
   }
   const float to_log2 = p.lse_is_log2 ? 1.f : kLog2e;
   float M = -INFINITY;
-  for (int i = 0; i < n_parts; ++i) {
-    const long li = p.part_major ? static_cast<long>(i) * p.rows + row : static_cast<long>(row) * p.max_parts + i;
-    M = fmaxf(M, p.parts_lse[li] * to_log2);
-  }
+  // part i of this row: (lse index, o index / 128)
+  auto lse_at = [&](int i) -> float {
+    return p.part_major ? p.parts_lse[static_cast<long>(i) * p.part_stride_lse + row]
+                        : p.parts_lse[static_cast<long>(row) * p.max_parts + i];
+  };
+  auto o_at = [&](int i) -> float {
+    return p.part_major ? p.parts_o[static_cast<long>(i) * p.part_stride_o + static_cast<long>(row) * kHeadDim + d]
+                        : p.parts_o[(static_cast<long>(row) * p.max_parts + i) * kHeadDim + d];
+  };
+  for (int i = 0; i < n_parts; ++i) M = fmaxf(M, lse_at(i) * to_log2);
   float W = 0.f, o = 0.f;
   if (M != -INFINITY) {
     for (int i = 0; i < n_parts; ++i) {
-      const long li = p.part_major ? static_cast<long>(i) * p.rows + row : static_cast<long>(row) * p.max_parts + i;
-      const float w = exp2f(p.parts_lse[li] * to_log2 - M);
+      const float w = exp2f(lse_at(i) * to_log2 - M);
       W += w;
-      o += w * p.parts_o[li * kHeadDim + d];
+      o += w * o_at(i);
     }
   }
   const float res = (W > 0.f) ? o / W : 0.f;

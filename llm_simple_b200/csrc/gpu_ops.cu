@@ -406,8 +406,8 @@ int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial
   return GPU_OPS_OK;
 }
 
-int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_parts, int n_parts, int rows,
-                             int head_dim, int dt, gpu_stream_t stream) {
+static int merge_parts(void *out, const float *o_parts, const float *lse_parts, long stride_o, long stride_lse,
+                       int n_parts, int rows, int head_dim, int dt, gpu_stream_t stream) {
   if (int rc = check_common(dt, head_dim)) return rc;
   if (!out || !o_parts || !lse_parts) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
   if (n_parts <= 0 || rows < 0) return fail(GPU_OPS_E_INVALID, "n_parts %d, rows %d", n_parts, rows);
@@ -415,6 +415,8 @@ int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_p
   p.out = out;
   p.parts_o = o_parts;
   p.parts_lse = lse_parts;
+  p.part_stride_o = stride_o;
+  p.part_stride_lse = stride_lse;
   p.part_major = 1;
   p.lse_is_log2 = 0;
   p.rows = rows;
@@ -429,6 +431,19 @@ int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_p
   if (e != cudaSuccess) return cuda_fail(e, "merge launch");
   g_launches += 1;
   return GPU_OPS_OK;
+}
+
+int gpu_attn_merge_lse_layer(void *out, const float *o_parts, const float *lse_parts, int n_parts, int rows,
+                             int head_dim, int dt, gpu_stream_t stream) {
+  return merge_parts(out, o_parts, lse_parts, static_cast<long>(rows) * 128, rows, n_parts, rows, head_dim, dt, stream);
+}
+
+int gpu_attn_merge_packed_layer(void *out, const float *parts, int n_parts, int rows, int head_dim, int dt,
+                                gpu_stream_t stream) {
+  if (!parts) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  const long stride = static_cast<long>(rows) * (128 + 1);
+  return merge_parts(out, parts, parts + static_cast<long>(rows) * 128, stride, stride, n_parts, rows, head_dim, dt,
+                     stream);
 }
 
 int gpu_ops_set_workspace(void *workspace, size_t bytes) {

@@ -76,9 +76,10 @@ struct MergeParams {
   void *out;               // dtype, element (row, d) at row_off(row) + d; may be NULL
   float *o_partial;        // fp32 [rows][128] or NULL
   float *lse_partial;      // natural log
-  const float *parts_o;    // [rows][max_parts][128] (part_major == 0) or [parts][rows][128]
+  const float *parts_o;    // [rows][max_parts][128] (part_major == 0) or part i at parts_o + i*part_stride_o
   const float *parts_lse;
   int part_major;
+  long part_stride_o, part_stride_lse; // part_major: elements between consecutive parts
   int lse_is_log2;         // workspace partials are in the log2 domain
   int rows, max_parts;
   // number of valid parts per row: fixed n_parts, or ceil(total_b / chunk)

@@ -20,7 +20,7 @@ _lib = None
 EXPORTS = [
     "gpu_flash_attn_layer", "gpu_flash_attn_gqa_layer", "gpu_flash_attn_opt_prefill_layer",
     "gpu_rope_layer", "gpu_rope_single_layer", "gpu_rope_kv_append_layer", "gpu_attn_prefill_layer",
-    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer",
+    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
 ]
@@ -90,6 +90,7 @@ def lib():
         L.gpu_attn_decode_workspace_bytes.argtypes = [dp, i]
         L.gpu_attn_decode_workspace_bytes.restype = ctypes.c_size_t
         L.gpu_attn_merge_lse_layer.argtypes = [vp, f32p, f32p, i, i, i, i, vp]
+        L.gpu_attn_merge_packed_layer.argtypes = [vp, f32p, i, i, i, i, vp]
         L.gpu_ops_set_workspace.argtypes = [vp, ctypes.c_size_t]
         L.gpu_attn_set_decode_chunk.argtypes = [i]
         L.gpu_attn_set_prefill_kernel.argtypes = [i]
@@ -193,6 +194,10 @@ def gpu_attn_decode_layer_noalloc(desc, out, q_in, k_in, v_in, k_cache, v_cache,
 def gpu_attn_merge_lse_layer(out, o_parts, lse_parts, n_parts, rows, head_dim, dt, stream=None):
     _check(lib().gpu_attn_merge_lse_layer(_ptr(out), _ptr(o_parts), _ptr(lse_parts), n_parts, rows,
                                           head_dim, dt, _stream(stream)))
+
+
+def gpu_attn_merge_packed_layer(out, parts, n_parts, rows, head_dim, dt, stream=None):
+    _check(lib().gpu_attn_merge_packed_layer(_ptr(out), _ptr(parts), n_parts, rows, head_dim, dt, _stream(stream)))
 
 
 def gpu_ops_set_workspace(workspace, nbytes):

@@ -1,0 +1,115 @@
+"""Two ranks, one GPU each (NCCL): KV-head sharding reproduces the single-device
+result bit for bit with no collective on the data path, and decode over a cache
+sharded by position (the one exchange: an all-gather of (O, LSE) partials) agrees
+with the oracle.  Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests.gpu_util import BF16, D, assert_parity, dev, host, rnd_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _case():
+    dt, H, kvh, neox, theta = BF16, 40, 8, True, 1e6
+    lens = [1500, 700, 2047, 33]
+    max_pos = 2056
+    table = orc.init_freq_cis(D, max_pos, theta, dt)
+    batch = len(lens)
+    q = rnd_bits((batch, H * D), dt, 1)
+    k, v = rnd_bits((batch, kvh * D), dt, 2), rnd_bits((batch, kvh * D), dt, 3)
+    kc = rnd_bits((batch, kvh, max_pos, D), dt, 4)      # head-major
+    vc = rnd_bits((batch, kvh, max_pos, D), dt, 5)
+    return dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc
+
+
+def _decode(ops, dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc):
+    batch = len(lens)
+    desc = ops.make_desc(dt, batch, H, kvh, 1, max_pos, layout="head", is_neox=neox)
+    ops.gpu_attn_set_decode_chunk(512)   # same split size whatever the head count per device
+    ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, max(lens) + 1)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    out = torch.empty((batch, H * D), dtype=torch.bfloat16, device="cuda")
+    ops.gpu_attn_decode_layer(desc, out, None, None, dev(q, dt), dev(k, dt), dev(v, dt), dev(kc, dt), dev(vc, dt),
+                              torch.from_numpy(table).cuda(), torch.tensor(lens, dtype=torch.int32, device="cuda"),
+                              None, True, max(lens) + 1, ws, ws_bytes)
+    torch.cuda.synchronize()
+    ops.gpu_attn_set_decode_chunk(0)
+    return host(out)
+
+
+def _rank_main(rank, world, port, ret):
+    import torch.distributed as dist
+    from llm_simple_b200 import ops, sharding
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc = _case()
+        batch, g = len(lens), H // kvh
+        # ---- (1) KV-head sharding: this rank's heads only, no collective on the data path
+        lo, hi = sharding.kv_head_range(kvh, world, rank)
+        qs = np.ascontiguousarray(q.reshape(batch, H, D)[:, lo * g:hi * g].reshape(batch, -1))
+        ks = np.ascontiguousarray(k.reshape(batch, kvh, D)[:, lo:hi].reshape(batch, -1))
+        vs = np.ascontiguousarray(v.reshape(batch, kvh, D)[:, lo:hi].reshape(batch, -1))
+        mine = _decode(ops, dt, (hi - lo) * g, hi - lo, neox, lens, max_pos, table, qs, ks, vs,
+                       np.ascontiguousarray(kc[:, lo:hi]), np.ascontiguousarray(vc[:, lo:hi]))
+        gathered = [torch.empty(mine.shape, dtype=torch.int16, device="cuda") for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(mine.view(np.int16)).cuda())   # test plumbing only
+        sharded = np.concatenate([t.cpu().numpy().view(np.uint16).reshape(batch, -1, D) for t in gathered], axis=1)
+        # ---- (2) cache sharded by position, one sequence, partial (O, LSE) exchange
+        total_old = lens[0]
+        sl_lo, sl_hi = sharding.position_slices(total_old, world)[rank]
+        local_max = sl_hi - sl_lo + 8
+        kl = np.zeros((1, kvh, local_max, D), np.uint16)
+        vl = np.zeros((1, kvh, local_max, D), np.uint16)
+        kl[0, :, :sl_hi - sl_lo], vl[0, :, :sl_hi - sl_lo] = kc[0, :, sl_lo:sl_hi], vc[0, :, sl_lo:sl_hi]
+        desc = ops.make_desc(dt, 1, H, kvh, 1, local_max, layout="head", is_neox=neox)
+        dec = sharding.SplitKVDecoder(desc, dt)
+        ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, local_max)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+        out = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
+        dec.step(out, dev(q[:1], dt), dev(k[:1], dt), dev(v[:1], dt), dev(kl, dt), dev(vl, dt),
+                 torch.from_numpy(table).cuda(), torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
+                 torch.tensor([total_old], dtype=torch.int32, device="cuda"), sl_hi - sl_lo, ws, ws_bytes)
+        torch.cuda.synchronize()
+        ret[rank] = (sharded, host(out))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_head_sharding_and_split_kv_exchange():
+    import torch.multiprocessing as mp
+    from llm_simple_b200 import ops
+    world, port = 2, _free_port()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_rank_main, args=(world, port, ret), nprocs=world, join=True)
+    dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc = _case()
+    single = _decode(ops, dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc)
+    sharded0, split0 = ret[0]
+    sharded1, split1 = ret[1]
+    # head-sharded == single device, bit for bit (same kernel, disjoint heads, same split size)
+    assert np.array_equal(sharded0.reshape(single.shape), single)
+    assert np.array_equal(sharded1.reshape(single.shape), single)
+    # position-sharded decode of sequence 0 vs the oracle; both ranks hold the full result
+    kc_t = np.ascontiguousarray(kc[0].transpose(1, 0, 2)).reshape(max_pos, kvh * D)
+    vc_t = np.ascontiguousarray(vc[0].transpose(1, 0, 2)).reshape(max_pos, kvh * D)
+    L = lens[0]
+    q_r = orc.rope_single_layer(q[:1], table, L, H, neox, dt)
+    k_r = orc.rope_single_layer(k[:1], table, L, kvh, neox, dt)
+    orc.kv_append(kc_t, vc_t, k_r, v[:1], L, kvh, D)
+    gold = orc.attn(q_r, kc_t, vc_t, 1, L + 1, L, H // kvh, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
+    assert_parity(split0, gold, dt, "rank 0")
+    assert np.array_equal(split0, split1)
