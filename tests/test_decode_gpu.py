@@ -62,7 +62,7 @@ def test_fused_decode_step(ops, dt, neox, theta, layout, H, kvh, lens, chunk):
     try:
         max_kv = max(lens) + 1
         ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, max_kv)
-        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
         ops.gpu_attn_decode_layer(desc, out, None, None, dev(q, dt), dev(k_new, dt), dev(v_new, dt), kc_d, vc_d,
                                   torch.from_numpy(table).cuda(), lens_d, None, True, max_kv, ws, ws_bytes)
         torch.cuda.synchronize()
@@ -103,7 +103,7 @@ def test_decode_steps_in_a_row_match_prefill_of_the_whole_sequence(ops):
     assert_parity(host(out_p), gold[:prompt], dt, "prefill")
     desc_d = ops.make_desc(dt, 1, H, kvh, 1, max_pos, layout="head", is_neox=neox)
     ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc_d, max_pos)
-    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
     out_d = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
     for s in range(steps):
         pos = prompt + s
@@ -146,7 +146,7 @@ def test_partial_outputs_merge_across_slices_like_one_device(ops, parts):
         last = p == parts - 1          # the owner of the tail appends the new token
         lens_d = torch.tensor([hi - lo], dtype=torch.int32, device="cuda")
         ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, local_max)
-        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
         ops.gpu_attn_decode_layer(desc, None, o_parts[p], lse_parts[p], dev(q, dt),
                                   dev(k_new, dt) if last else None, dev(v_new, dt) if last else None, kl_d, vl_d,
                                   tab_d, lens_d, rope_pos, last, hi - lo + 1, ws, ws_bytes)
@@ -165,7 +165,7 @@ def test_empty_slice_gives_minus_inf_lse_and_is_ignored_by_the_merge(ops):
     o = torch.full((2, H, D), 7.0, dtype=torch.float32, device="cuda")
     lse = torch.zeros((2, H), dtype=torch.float32, device="cuda")
     zero = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ws = torch.empty(1 << 16, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     ops.gpu_attn_decode_layer(desc, None, o[0], lse[0], q, None, None, kc, kc, table, zero, zero, False, 1, ws,
                               ws.numel())
     torch.cuda.synchronize()

@@ -39,7 +39,7 @@ def _decode(ops, dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc):
     desc = ops.make_desc(dt, batch, H, kvh, 1, max_pos, layout="head", is_neox=neox)
     ops.gpu_attn_set_decode_chunk(512)   # same split size whatever the head count per device
     ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, max(lens) + 1)
-    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
     out = torch.empty((batch, H * D), dtype=torch.bfloat16, device="cuda")
     ops.gpu_attn_decode_layer(desc, out, None, None, dev(q, dt), dev(k, dt), dev(v, dt), dev(kc, dt), dev(vc, dt),
                               torch.from_numpy(table).cuda(), torch.tensor(lens, dtype=torch.int32, device="cuda"),
@@ -65,9 +65,10 @@ def _rank_main(rank, world, port, ret):
         vs = np.ascontiguousarray(v.reshape(batch, kvh, D)[:, lo:hi].reshape(batch, -1))
         mine = _decode(ops, dt, (hi - lo) * g, hi - lo, neox, lens, max_pos, table, qs, ks, vs,
                        np.ascontiguousarray(kc[:, lo:hi]), np.ascontiguousarray(vc[:, lo:hi]))
-        gathered = [torch.empty(mine.shape, dtype=torch.int16, device="cuda") for _ in range(world)]
-        dist.all_gather(gathered, torch.from_numpy(mine.view(np.int16)).cuda())   # test plumbing only
-        sharded = np.concatenate([t.cpu().numpy().view(np.uint16).reshape(batch, -1, D) for t in gathered], axis=1)
+        mine_d = dev(mine, dt)
+        gathered = [torch.empty_like(mine_d) for _ in range(world)]
+        dist.all_gather(gathered, mine_d)                                         # test plumbing only
+        sharded = np.concatenate([host(t).reshape(batch, -1, D) for t in gathered], axis=1)
         # ---- (2) cache sharded by position, one sequence, partial (O, LSE) exchange
         total_old = lens[0]
         sl_lo, sl_hi = sharding.position_slices(total_old, world)[rank]
@@ -78,7 +79,7 @@ def _rank_main(rank, world, port, ret):
         desc = ops.make_desc(dt, 1, H, kvh, 1, local_max, layout="head", is_neox=neox)
         dec = sharding.SplitKVDecoder(desc, dt)
         ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, local_max)
-        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
         out = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
         dec.step(out, dev(q[:1], dt), dev(k[:1], dt), dev(v[:1], dt), dev(kl, dt), dev(vl, dt),
                  torch.from_numpy(table).cuda(), torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
