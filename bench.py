@@ -205,6 +205,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling on a small case)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch (profiling on a small case)")
     ap.add_argument("--no-extras", action="store_true", help="skip prefill leg, e2e and CPU baseline")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill"],
+                    help="prefill: run only the prefill leg (small, for profiling) and print its object")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -233,6 +235,19 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ops.lib()
     pk = peaks()
+
+    def barrier0():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.leg == "prefill":
+        res = prefill_leg(torch, ops, orc, world, torch.device("cuda", local_rank), barrier0, pk)
+        if rank == 0:
+            print(json.dumps({"prefill": res}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     H, kvh = cfg["n_heads"], cfg["n_kv_heads"]
     if kvh % world:

@@ -3,19 +3,26 @@
 // shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), online softmax
 // in registers.
 //
-// One CTA = 128 query rows of one head of one sequence, walking the KV cache in
-// tiles of 128 positions up to the causal diagonal.
-//   warp 0        TMA producer (one elected lane): Q once, then K and V tiles
-//                 into two-stage rings
-//   warp 1        MMA issuer (one elected lane): S = Q.K^T (operands from shared
-//                 memory) into one of two TMEM buffers, then O += P.V with P
-//                 read from TMEM and V from shared memory (N-major operand)
-//   warps 2-5     softmax, one thread per query row (TMEM lane): tcgen05.ld of
-//                 the S row, running max / sum in the log2 domain, P written
-//                 back over S as packed 16-bit pairs (tcgen05.st); O is only
-//                 rescaled when the running max has grown by more than 2^8
-//                 since the last rescale; epilogue O / l -> global memory
-// S for tile j+1 is computed while the softmax of tile j runs.
+// One CTA = 256 query rows (two tiles A and B of 128) of one head of one
+// sequence, walking the KV cache in tiles of 128 positions up to the causal
+// diagonal.  Twelve warps in three groups of four:
+//   warp 0        TMA producer (one elected lane): Q tiles once, then K and V
+//                 tiles into two-stage rings
+//   warp 1        MMA issuer (one elected lane): S_X = Q_X.K^T (operands from
+//                 shared memory) into TMEM, then O_X += P_X.V with P_X read from
+//                 TMEM and V from shared memory (N-major operand); per KV tile
+//                 it issues  P.V(A) Q.K(A,next)  P.V(B) Q.K(B,next), so that the
+//                 tensor pipe works for one query tile while the other one's
+//                 softmax runs
+//   warps 2-3     idle (they only give their registers away)
+//   warps 4-7     softmax of tile A, warps 8-11 softmax of tile B: one thread
+//                 per query row (TMEM lane): tcgen05.ld of the S row, running
+//                 max / sum in the log2 domain, P written back over S as packed
+//                 16-bit pairs (tcgen05.st); O is only rescaled when the running
+//                 max has grown by more than 2^8 since the last rescale;
+//                 epilogue O / l -> global memory
+// TMEM (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each; P_X aliases
+// the first 64 columns of S_X.
 //
 // Reference semantics: tests/flash_attn_test.cpp:106-192 (mask col > row+offset,
 // scale 1/sqrt(D) folded into the exponent, O = softmax(S).V, out [m][H*D]).
@@ -34,24 +41,24 @@ namespace b200attn {
 
 namespace tc5 {
 
-constexpr int kBM = 128;            // query rows per CTA
+constexpr int kBM = 128;            // query rows per tile; two tiles per CTA
 constexpr int kBN = 128;            // key positions per tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 384;
 constexpr int kStages = 2;
 constexpr uint32_t kHalfTile = 128 * 128;        // bytes of a [128 rows][64 elem] swizzled half tile
 constexpr uint32_t kTileBytes = 2 * kHalfTile;   // [128][128] 16-bit
-constexpr uint32_t kSmemQ = 0;
-constexpr uint32_t kSmemK = kSmemQ + kTileBytes;
+constexpr uint32_t kSmemQ = 0;                   // Q_A, Q_B
+constexpr uint32_t kSmemK = kSmemQ + 2 * kTileBytes;
 constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
 constexpr uint32_t kSmemBar = kSmemV + kStages * kTileBytes;
 constexpr uint32_t kSmemTotal = kSmemBar + 256 + 1024; // barriers + slack for 1024-byte alignment
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+constexpr uint32_t kColS = 0, kColO = 256;       // S_X at kColS + 128 X, O_X at kColO + 128 X
 constexpr float kRescaleThreshold = 8.0f;        // log2 domain
 
-// barrier slots (8 bytes each) inside the barrier block
+// barrier slots (8 bytes each) inside the barrier block; X = 0 (tile A) or 1 (tile B)
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_COUNT = 14 };
+       BAR_ODONE = 13, BAR_COUNT = 15 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -182,6 +189,13 @@ struct Params {
   int *error_flag;
 };
 
+template <int R> __device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
+}
+template <int R> __device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -195,26 +209,28 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   auto bar = [&](int i) { return bar_base + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / p.group;
-  const int row0 = qt * kBM;
-  const int row_end = min(p.m, row0 + kBM);
-  const int kv_end = min(p.n, p.offset + row_end);
-  const int ntiles = (kv_end + kBN - 1) / kBN;
-  constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  const int row0 = qb * 2 * kBM;                 // first row of tile A; tile B starts kBM later
+  const bool has_b = row0 + kBM < p.m;
+  // KV tiles each query tile needs (up to its causal diagonal / the end of the cache)
+  const int nt_a = (min(p.n, p.offset + min(p.m, row0 + kBM)) + kBN - 1) / kBN;
+  const int nt_b = has_b ? (min(p.n, p.offset + min(p.m, row0 + 2 * kBM)) + kBN - 1) / kBN : 0;
+  const int nt = max(nt_a, nt_b);
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t idesc_qk = instr_desc(fmt, 0), idesc_pv = instr_desc(fmt, 1);
 
   if (threadIdx.x == 0) {
     mbar_init(bar(BAR_Q), 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_KFULL + s), 1);
       mbar_init(bar(BAR_KEMPTY + s), 1);
       mbar_init(bar(BAR_VFULL + s), 1);
       mbar_init(bar(BAR_VEMPTY + s), 1);
       mbar_init(bar(BAR_SFULL + s), 1);
       mbar_init(bar(BAR_PREADY + s), 128);
+      mbar_init(bar(BAR_ODONE + s), 1);
     }
-    mbar_init(bar(BAR_ODONE), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -231,13 +247,16 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      mbar_expect_tx(bar(BAR_Q), kTileBytes);
-      tma_load_4d(smem_base + kSmemQ, &map_q, bar(BAR_Q), 0, h, row0, b);
-      tma_load_4d(smem_base + kSmemQ + kHalfTile, &map_q, bar(BAR_Q), 64, h, row0, b);
-      for (int j = 0; j < ntiles; ++j) {
+  if (warp < 4) {
+    reg_dec<56>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------- TMA producer
+      mbar_expect_tx(bar(BAR_Q), has_b ? 2 * kTileBytes : kTileBytes);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x) {
+        tma_load_4d(smem_base + kSmemQ + x * kTileBytes, &map_q, bar(BAR_Q), 0, h, row0 + x * kBM, b);
+        tma_load_4d(smem_base + kSmemQ + x * kTileBytes + kHalfTile, &map_q, bar(BAR_Q), 64, h, row0 + x * kBM, b);
+      }
+      for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
         if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) break;
@@ -249,81 +268,105 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tma_load_4d(smem_base + kSmemV + s * kTileBytes, &map_v, bar(BAR_VFULL + s), 0, j * kBN, kvh, b);
         tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, &map_v, bar(BAR_VFULL + s), 64, j * kBN, kvh, b);
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------- MMA issuer
       bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_flag, 3);
-      auto issue_qk = [&](int j) -> bool {
+      // S_X = Q_X . K[j]^T ; `last` marks the last reader of K[j], which frees the stage
+      auto issue_qk = [&](int x, int j, bool last) -> bool {
         const int s = j % kStages;
         if (!mbar_wait(bar(BAR_KFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 4)) return false;
         tc_fence_after();
-        const uint32_t d = tmem + ((j & 1) ? kColS1 : kColS0);
+        const uint32_t d = tmem + kColS + 128 * x;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t koff = (k >> 2) * kHalfTile + (k & 3) * 32;
-          tc_mma_ss(d, smem_desc(smem_base + kSmemQ + koff, 16, 1024),
+          tc_mma_ss(d, smem_desc(smem_base + kSmemQ + x * kTileBytes + koff, 16, 1024),
                     smem_desc(smem_base + kSmemK + s * kTileBytes + koff, 16, 1024), idesc_qk, k > 0);
         }
-        tc_commit(bar(BAR_KEMPTY + s));
-        tc_commit(bar(BAR_SFULL + (j & 1)));
+        if (last) tc_commit(bar(BAR_KEMPTY + s));
+        tc_commit(bar(BAR_SFULL + x));
         return true;
       };
-      if (ok) ok = issue_qk(0);
-      if (ok && ntiles > 1) ok = issue_qk(1);
-      for (int j = 0; ok && j < ntiles; ++j) {
+      // O_X += P_X . V[j] ; `last` marks the last reader of V[j]
+      auto issue_pv = [&](int x, int j, bool last) -> bool {
         const int s = j % kStages;
-        if (!mbar_wait(bar(BAR_PREADY + (j & 1)), (j >> 1) & 1, abort_flag, p.error_flag, 5)) break;
-        if (!mbar_wait(bar(BAR_VFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 6)) break;
+        if (!mbar_wait(bar(BAR_PREADY + x), j & 1, abort_flag, p.error_flag, 5)) return false;
+        if (!mbar_wait(bar(BAR_VFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 6)) return false;
         tc_fence_after();
-        const uint32_t pcol = tmem + ((j & 1) ? kColS1 : kColS0);
+        const uint32_t pcol = tmem + kColS + 128 * x;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // 16 positions per step: 8 TMEM columns of packed P, 16 rows (2048 B) of V
-          tc_mma_ts(tmem + kColO, pcol + 8 * k, smem_desc(smem_base + kSmemV + s * kTileBytes + k * 2048, kHalfTile, 1024),
-                    idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(tmem + kColO + 128 * x, pcol + 8 * k,
+                    smem_desc(smem_base + kSmemV + s * kTileBytes + k * 2048, kHalfTile, 1024), idesc_pv,
+                    (j > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(bar(BAR_VEMPTY + s));
-        tc_commit(bar(BAR_ODONE));
-        if (j + 2 < ntiles) ok = issue_qk(j + 2);
+        if (last) tc_commit(bar(BAR_VEMPTY + s));
+        tc_commit(bar(BAR_ODONE + x));
+        return true;
+      };
+      // tile B (when present) reads every KV tile that A reads, and reads it after A
+      if (ok && nt_a > 0) ok = issue_qk(0, 0, !has_b);
+      if (ok && has_b) ok = issue_qk(1, 0, true);
+      for (int j = 0; ok && j < nt; ++j) {
+        if (j < nt_a) {
+          ok = issue_pv(0, j, !has_b);
+          if (ok && j + 1 < nt_a) ok = issue_qk(0, j + 1, !has_b);
+        }
+        if (ok && has_b) {
+          ok = issue_pv(1, j, true);
+          if (ok && j + 1 < nt_b) ok = issue_qk(1, j + 1, true);
+        }
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue
+    reg_inc<224>();
+    // ------------------------------------------------------------ softmax + epilogue of tile X
+    const int x = (warp >> 2) - 1;               // 0: tile A (warps 4-7), 1: tile B (warps 8-11)
     const int quad = warp & 3;                   // TMEM lane quadrant this warp may touch
-    const int row_in_tile = quad * 32 + lane;
-    const int row = row0 + row_in_tile;          // query token index within the call
+    const int trow0 = row0 + x * kBM;
+    const int row = trow0 + quad * 32 + lane;    // query token index within the call
+    const int ntx = x == 0 ? nt_a : nt_b;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t scol = tmem + lane_addr + kColS + 128 * x;
+    const uint32_t ocol = tmem + lane_addr + kColO + 128 * x;
     const int vis_end = min(p.n, p.offset + row + 1); // columns < vis_end are visible to this row
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + (j & 1)), (j >> 1) & 1, abort_flag, p.error_flag, 7))) {
+    for (int j = 0; j < ntx; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + x), j & 1, abort_flag, p.error_flag, 7))) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t scol = tmem + lane_addr + ((j & 1) ? kColS1 : kColS0);
       uint32_t su[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld32(scol + 32 * c, su + 32 * c);
       tc_wait_ld();
       const int col0 = j * kBN;
       // only the last tiles of a row block cross the diagonal or the end of the cache
-      if (col0 + kBN > min(p.n, p.offset + row0 + 1)) {
+      if (col0 + kBN > min(p.n, p.offset + trow0 + 1)) {
 #pragma unroll
         for (int c = 0; c < 128; ++c)
           if (col0 + c >= vis_end) su[c] = 0xff800000u; // -inf
       }
-      float mx = __uint_as_float(su[0]);
+      // row max with eight independent chains
+      float mxa[8];
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(su[c]));
+      for (int i = 0; i < 8; ++i) mxa[i] = __uint_as_float(su[i]);
+#pragma unroll
+      for (int c = 8; c < 128; c += 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mxa[i] = fmaxf(mxa[i], __uint_as_float(su[c + i]));
+      }
+      float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                       fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
       mx *= p.scale_log2;
       // lazy rescale: keep the old reference max unless the new one is much larger
       const bool grow = mx > m_ref + kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow) && j > 0) {
         // O must hold every P.V issued so far before it is rescaled
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE), (j - 1) & 1, abort_flag, p.error_flag, 8))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + x), (j - 1) & 1, abort_flag, p.error_flag, 8))) {
           ok = false;
           break;
         }
@@ -333,41 +376,43 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tc_ld32(tmem + lane_addr + kColO + 32 * c, o);
+          tc_ld32(ocol + 32 * c, o);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tc_st32(tmem + lane_addr + kColO + 32 * c, o);
+          tc_st32(ocol + 32 * c, o);
         }
         tc_wait_st();
       }
       if (grow) m_ref = mx;
+      // P = 2^(s*scale - m_ref), packed pairs written back to TMEM half a tile at a time
       uint32_t pk[64];
-      float sum = 0.f;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_ref;
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        const float p0 = ex2(fmaf(__uint_as_float(su[2 * c]), p.scale_log2, -m_ref));
-        const float p1 = ex2(fmaf(__uint_as_float(su[2 * c + 1]), p.scale_log2, -m_ref));
-        sum += p0 + p1;
+        const float p0 = ex2(fmaf(__uint_as_float(su[2 * c]), p.scale_log2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(su[2 * c + 1]), p.scale_log2, neg_m));
+        sums[c & 3] += p0 + p1;
         pk[c] = Elem<T>::pack(p0, p1);
+        if (c == 31) tc_st32(scol, pk);
       }
-      l += sum;
-      tc_st32(scol, pk);
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
       tc_st32(scol + 32, pk + 32);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(BAR_PREADY + (j & 1)));
+      mbar_arrive(bar(BAR_PREADY + x));
     }
-    if (ok && ntiles > 0)
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE), (ntiles - 1) & 1, abort_flag, p.error_flag, 9));
-    if (ok) {
+    if (ok && ntx > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + x), (ntx - 1) & 1, abort_flag, p.error_flag, 9));
+    if (ok && ntx > 0) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       T *dst = static_cast<T *>(p.out) + b * p.out_seq + static_cast<long>(row) * p.out_tok + h * kHeadDim;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
-        tc_ld32(tmem + lane_addr + kColO + 32 * c, o);
+        tc_ld32(ocol + 32 * c, o);
         tc_wait_ld();
         if (row < p.m) {
 #pragma unroll
@@ -476,7 +521,7 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   kp.out_tok = g.out_tok;
   kp.scale_log2 = p.scale_log2;
   kp.error_flag = err_dev;
-  dim3 grid((p.m + kBM - 1) / kBM, g.n_heads, g.batch);
+  dim3 grid((p.m + 2 * kBM - 1) / (2 * kBM), g.n_heads, g.batch);
   cudaError_t e;
   if (bf16) {
     e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
