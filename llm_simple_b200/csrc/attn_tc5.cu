@@ -114,20 +114,26 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Shared-memory descriptors are passed as their low word (start address and LBO
+// fields) plus one high word shared by all operands (SBO, version, swizzle).
 // D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                          uint32_t idesc, uint32_t acc) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
       : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi,
+                                          uint32_t idesc, uint32_t acc) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
@@ -160,19 +166,16 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1, as two words.
 //   K-major operand  ([rows][64 elem] half tiles): LBO field 1 (unused), SBO = 1024 B (8 rows)
 //   MN-major operand (V: [pos][64 elem] half tiles): LBO = distance between the two 64-element
 //   halves, SBO = 1024 B (8 positions)
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((addr >> 4) & 0x3fff);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
-  d |= static_cast<uint64_t>(1) << 46;  // descriptor version (Blackwell)
-  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
-  return d;
+// low word: start address >> 4 in bits [0,14), LBO >> 4 in bits [16,30)
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr >> 4) & 0x3fffu) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
 }
+// high word: SBO >> 4 in bits [0,14), version 1 at bit 14, SWIZZLE_128B (2) at bits [29,32)
+constexpr uint32_t kDescHi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
 
 // Instruction descriptor, kind::f16: fp32 accumulate, A/B format fmt (0 fp16, 1 bf16), M = 128, N = 128.
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major) {
@@ -248,7 +251,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 4) {
-    reg_dec<56>();
+    reg_dec<64>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer
       mbar_expect_tx(bar(BAR_Q), has_b ? 2 * kTileBytes : kTileBytes);
@@ -271,17 +274,25 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- MMA issuer
       bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_flag, 3);
+      // Descriptors are built once; per instruction only a constant is added to the
+      // start-address field.  The issuing thread's own instruction count per MMA must
+      // stay well under the 64 cycles a 128x128x16 MMA takes, or the tensor pipe starves.
+      const uint32_t dq0 = smem_desc_lo(smem_base + kSmemQ, 16);
+      const uint32_t dk0 = smem_desc_lo(smem_base + kSmemK, 16);
+      const uint32_t dv0 = smem_desc_lo(smem_base + kSmemV, kHalfTile);
+      constexpr uint32_t kTileStep = kTileBytes >> 4; // one tile further, in descriptor address units
       // S_X = Q_X . K[j]^T ; `last` marks the last reader of K[j], which frees the stage
       auto issue_qk = [&](int x, int j, bool last) -> bool {
         const int s = j % kStages;
         if (!mbar_wait(bar(BAR_KFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 4)) return false;
         tc_fence_after();
         const uint32_t d = tmem + kColS + 128 * x;
+        const uint32_t dq = dq0 + x * kTileStep, dk = dk0 + s * kTileStep;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t koff = (k >> 2) * kHalfTile + (k & 3) * 32;
-          tc_mma_ss(d, smem_desc(smem_base + kSmemQ + x * kTileBytes + koff, 16, 1024),
-                    smem_desc(smem_base + kSmemK + s * kTileBytes + koff, 16, 1024), idesc_qk, k > 0);
+          constexpr uint32_t kHalfStep = kHalfTile >> 4;
+          const uint32_t ko = (k >> 2) * kHalfStep + (k & 3) * 2; // 16 elements = 32 bytes per step
+          tc_mma_ss(d, dq + ko, dk + ko, kDescHi, idesc_qk, k > 0);
         }
         if (last) tc_commit(bar(BAR_KEMPTY + s));
         tc_commit(bar(BAR_SFULL + x));
@@ -293,13 +304,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (!mbar_wait(bar(BAR_PREADY + x), j & 1, abort_flag, p.error_flag, 5)) return false;
         if (!mbar_wait(bar(BAR_VFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 6)) return false;
         tc_fence_after();
-        const uint32_t pcol = tmem + kColS + 128 * x;
+        const uint32_t pcol = tmem + kColS + 128 * x, ocol = tmem + kColO + 128 * x;
+        const uint32_t dv = dv0 + s * kTileStep;
+        const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // 16 positions per step: 8 TMEM columns of packed P, 16 rows (2048 B) of V
-          tc_mma_ts(tmem + kColO + 128 * x, pcol + 8 * k,
-                    smem_desc(smem_base + kSmemV + s * kTileBytes + k * 2048, kHalfTile, 1024), idesc_pv,
-                    (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(ocol, pcol + 8 * k, dv + k * (2048 >> 4), kDescHi, idesc_pv, k > 0 ? 1u : acc0);
         }
         if (last) tc_commit(bar(BAR_VEMPTY + s));
         tc_commit(bar(BAR_ODONE + x));
@@ -320,7 +331,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
     }
   } else {
-    reg_inc<224>();
+    reg_inc<216>();
     // ------------------------------------------------------------ softmax + epilogue of tile X
     const int x = (warp >> 2) - 1;               // 0: tile A (warps 4-7), 1: tile B (warps 8-11)
     const int quad = warp & 3;                   // TMEM lane quadrant this warp may touch
