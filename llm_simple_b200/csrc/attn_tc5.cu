@@ -3,14 +3,9 @@
 // shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), online softmax
 // in registers.
 //
-// Persistent: one CTA per SM loops over work items, longest first.  A work item
-// = 256 query rows (two tiles A and B of 128) of one head of one sequence,
-// walking the KV cache in tiles of 128 positions up to the causal diagonal.
-// TMEM is allocated once per CTA; barrier phases run on across items, so the
-// producer prefetches the next item's K/V (and its Q as soon as the last Q.K^T
-// of the current item has been issued) while the current item drains, and the
-// epilogue of one item overlaps the first MMAs of the next.
-// Twelve warps in three groups of four:
+// One CTA = 256 query rows (two tiles A and B of 128) of one head of one
+// sequence, walking the KV cache in tiles of 128 positions up to the causal
+// diagonal.  Twelve warps in three groups of four:
 //   warp 0        TMA producer (one elected lane): Q tiles once, then K and V
 //                 tiles into two-stage rings
 //   warp 1        MMA issuer (one elected lane): S_X = Q_X.K^T (operands from
@@ -62,8 +57,8 @@ constexpr uint32_t kColS = 0, kColO = 256;       // S_X at kColS + 128 X, O_X at
 constexpr float kRescaleThreshold = 8.0f;        // log2 domain
 
 // barrier slots (8 bytes each) inside the barrier block; X = 0 (tile A) or 1 (tile B)
-enum { BAR_QFULL = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_OFREE = 15, BAR_QEMPTY = 17, BAR_COUNT = 18 };
+enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
+       BAR_ODONE = 13, BAR_COUNT = 15 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -192,7 +187,6 @@ struct Params {
   void *out;
   int m, n, offset;
   int group;
-  int n_heads, batch, n_qblocks; // work items = n_qblocks * n_heads * batch
   long out_seq, out_tok;
   float scale_log2;
   int *error_flag;
@@ -203,30 +197,6 @@ template <int R> __device__ __forceinline__ void reg_dec() {
 }
 template <int R> __device__ __forceinline__ void reg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
-}
-
-// One work item and what each role derives from it (identically).
-struct Item {
-  int qb, h, b, kvh;
-  int row0;        // first query row of tile A; tile B starts kBM rows later
-  bool has_b;
-  int nt_a, nt_b, nt; // KV tiles needed by tile A, tile B, and their maximum
-};
-
-__device__ __forceinline__ Item make_item(const Params &p, int w) {
-  Item it;
-  const int per_q = p.n_heads * p.batch;
-  it.qb = p.n_qblocks - 1 - w / per_q;   // longest (last) query block first
-  const int rest = w % per_q;
-  it.h = rest % p.n_heads;
-  it.b = rest / p.n_heads;
-  it.kvh = it.h / p.group;
-  it.row0 = it.qb * 2 * kBM;
-  it.has_b = it.row0 + kBM < p.m;
-  it.nt_a = (min(p.n, p.offset + min(p.m, it.row0 + kBM)) + kBN - 1) / kBN;
-  it.nt_b = it.has_b ? (min(p.n, p.offset + min(p.m, it.row0 + 2 * kBM)) + kBN - 1) / kBN : 0;
-  it.nt = max(it.nt_a, it.nt_b);
-  return it;
 }
 
 template <typename T>
@@ -242,13 +212,19 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   auto bar = [&](int i) { return bar_base + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_items = p.n_qblocks * p.n_heads * p.batch;
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / p.group;
+  const int row0 = qb * 2 * kBM;                 // first row of tile A; tile B starts kBM later
+  const bool has_b = row0 + kBM < p.m;
+  // KV tiles each query tile needs (up to its causal diagonal / the end of the cache)
+  const int nt_a = (min(p.n, p.offset + min(p.m, row0 + kBM)) + kBN - 1) / kBN;
+  const int nt_b = has_b ? (min(p.n, p.offset + min(p.m, row0 + 2 * kBM)) + kBN - 1) / kBN : 0;
+  const int nt = max(nt_a, nt_b);
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t idesc_qk = instr_desc(fmt, 0), idesc_pv = instr_desc(fmt, 1);
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(BAR_QFULL), 1);
-    mbar_init(bar(BAR_QEMPTY), 1);
+    mbar_init(bar(BAR_Q), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_KFULL + s), 1);
       mbar_init(bar(BAR_KEMPTY + s), 1);
@@ -257,7 +233,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar(BAR_SFULL + s), 1);
       mbar_init(bar(BAR_PREADY + s), 128);
       mbar_init(bar(BAR_ODONE + s), 1);
-      mbar_init(bar(BAR_OFREE + s), 128);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -279,40 +254,26 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     reg_dec<64>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer
-      uint32_t kv = 0;    // K/V tiles loaded so far (ring position), across items
-      uint32_t n_it = 0;  // items started so far
-      bool ok = true;
-      auto load_kv = [&](const Item &it, int j) -> bool {
-        const int s = kv & 1;
-        const uint32_t ph = (kv >> 1) & 1;
-        if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) return false;
+      mbar_expect_tx(bar(BAR_Q), has_b ? 2 * kTileBytes : kTileBytes);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x) {
+        tma_load_4d(smem_base + kSmemQ + x * kTileBytes, &map_q, bar(BAR_Q), 0, h, row0 + x * kBM, b);
+        tma_load_4d(smem_base + kSmemQ + x * kTileBytes + kHalfTile, &map_q, bar(BAR_Q), 64, h, row0 + x * kBM, b);
+      }
+      for (int j = 0; j < nt; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) break;
         mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
-        tma_load_4d(smem_base + kSmemK + s * kTileBytes, &map_k, bar(BAR_KFULL + s), 0, j * kBN, it.kvh, it.b);
-        tma_load_4d(smem_base + kSmemK + s * kTileBytes + kHalfTile, &map_k, bar(BAR_KFULL + s), 64, j * kBN, it.kvh, it.b);
-        if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2)) return false;
+        tma_load_4d(smem_base + kSmemK + s * kTileBytes, &map_k, bar(BAR_KFULL + s), 0, j * kBN, kvh, b);
+        tma_load_4d(smem_base + kSmemK + s * kTileBytes + kHalfTile, &map_k, bar(BAR_KFULL + s), 64, j * kBN, kvh, b);
+        if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2)) break;
         mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
-        tma_load_4d(smem_base + kSmemV + s * kTileBytes, &map_v, bar(BAR_VFULL + s), 0, j * kBN, it.kvh, it.b);
-        tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, &map_v, bar(BAR_VFULL + s), 64, j * kBN, it.kvh, it.b);
-        ++kv;
-        return true;
-      };
-      for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ++n_it) {
-        const Item it = make_item(p, w);
-        // the first K/V tile does not depend on the Q buffer: request it before waiting for that
-        ok = load_kv(it, 0);
-        if (!ok) break;
-        // Q buffer is free once the last Q.K^T of the previous item has been executed
-        if (!mbar_wait(bar(BAR_QEMPTY), (n_it & 1) ^ 1, abort_flag, p.error_flag, 10)) break;
-        mbar_expect_tx(bar(BAR_QFULL), it.has_b ? 2 * kTileBytes : kTileBytes);
-        for (int x = 0; x < (it.has_b ? 2 : 1); ++x) {
-          tma_load_4d(smem_base + kSmemQ + x * kTileBytes, &map_q, bar(BAR_QFULL), 0, it.h, it.row0 + x * kBM, it.b);
-          tma_load_4d(smem_base + kSmemQ + x * kTileBytes + kHalfTile, &map_q, bar(BAR_QFULL), 64, it.h,
-                      it.row0 + x * kBM, it.b);
-        }
-        for (int j = 1; ok && j < it.nt; ++j) ok = load_kv(it, j);
+        tma_load_4d(smem_base + kSmemV + s * kTileBytes, &map_v, bar(BAR_VFULL + s), 0, j * kBN, kvh, b);
+        tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, &map_v, bar(BAR_VFULL + s), 64, j * kBN, kvh, b);
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- MMA issuer
+      bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag, p.error_flag, 3);
       // Descriptors are built once; per instruction only a constant is added to the
       // start-address field.  The issuing thread's own instruction count per MMA must
       // stay well under the 64 cycles a 128x128x16 MMA takes, or the tensor pipe starves.
@@ -320,14 +281,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const uint32_t dk0 = smem_desc_lo(smem_base + kSmemK, 16);
       const uint32_t dv0 = smem_desc_lo(smem_base + kSmemV, kHalfTile);
       constexpr uint32_t kTileStep = kTileBytes >> 4; // one tile further, in descriptor address units
-      uint32_t kv = 0;           // K/V tiles consumed so far (ring position), across items
-      uint32_t nx[2] = {0, 0};   // tiles of A / B processed so far, across items (barrier phases)
-      uint32_t n_it = 0;
-      bool ok = true;
-      // S_X = Q_X . K^T of ring slot `kvi`; `last` marks the last reader of that K tile
-      auto issue_qk = [&](int x, uint32_t kvi, bool last) -> bool {
-        const int s = kvi & 1;
-        if (!mbar_wait(bar(BAR_KFULL + s), (kvi >> 1) & 1, abort_flag, p.error_flag, 4)) return false;
+      // S_X = Q_X . K[j]^T ; `last` marks the last reader of K[j], which frees the stage
+      auto issue_qk = [&](int x, int j, bool last) -> bool {
+        const int s = j % kStages;
+        if (!mbar_wait(bar(BAR_KFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 4)) return false;
         tc_fence_after();
         const uint32_t d = tmem + kColS + 128 * x;
         const uint32_t dq = dq0 + x * kTileStep, dk = dk0 + s * kTileStep;
@@ -341,15 +298,15 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tc_commit(bar(BAR_SFULL + x));
         return true;
       };
-      // O_X += P_X . V of ring slot `kvi`; `first` overwrites O_X; `last` marks the last reader of V
-      auto issue_pv = [&](int x, uint32_t kvi, bool first, bool last) -> bool {
-        const int s = kvi & 1;
-        if (!mbar_wait(bar(BAR_PREADY + x), nx[x] & 1, abort_flag, p.error_flag, 5)) return false;
-        if (!mbar_wait(bar(BAR_VFULL + s), (kvi >> 1) & 1, abort_flag, p.error_flag, 6)) return false;
+      // O_X += P_X . V[j] ; `last` marks the last reader of V[j]
+      auto issue_pv = [&](int x, int j, bool last) -> bool {
+        const int s = j % kStages;
+        if (!mbar_wait(bar(BAR_PREADY + x), j & 1, abort_flag, p.error_flag, 5)) return false;
+        if (!mbar_wait(bar(BAR_VFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 6)) return false;
         tc_fence_after();
         const uint32_t pcol = tmem + kColS + 128 * x, ocol = tmem + kColO + 128 * x;
         const uint32_t dv = dv0 + s * kTileStep;
-        const uint32_t acc0 = first ? 0u : 1u;
+        const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // 16 positions per step: 8 TMEM columns of packed P, 16 rows (2048 B) of V
@@ -357,40 +314,20 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         if (last) tc_commit(bar(BAR_VEMPTY + s));
         tc_commit(bar(BAR_ODONE + x));
-        ++nx[x];
         return true;
       };
-      for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x, ++n_it) {
-        const Item it = make_item(p, w);
-        const bool has_b = it.has_b;
-        ok = mbar_wait(bar(BAR_QFULL), n_it & 1, abort_flag, p.error_flag, 3);
-        // tile B (when present) reads every KV tile that A reads, and reads it after A
-        if (ok) ok = issue_qk(0, kv, !has_b);
-        if (ok && it.nt_a == 1 && !has_b) tc_commit(bar(BAR_QEMPTY));
+      // tile B (when present) reads every KV tile that A reads, and reads it after A
+      if (ok && nt_a > 0) ok = issue_qk(0, 0, !has_b);
+      if (ok && has_b) ok = issue_qk(1, 0, true);
+      for (int j = 0; ok && j < nt; ++j) {
+        if (j < nt_a) {
+          ok = issue_pv(0, j, !has_b);
+          if (ok && j + 1 < nt_a) ok = issue_qk(0, j + 1, !has_b);
+        }
         if (ok && has_b) {
-          ok = issue_qk(1, kv, true);
-          if (ok && it.nt_b == 1) tc_commit(bar(BAR_QEMPTY));
+          ok = issue_pv(1, j, true);
+          if (ok && j + 1 < nt_b) ok = issue_qk(1, j + 1, true);
         }
-        for (int j = 0; ok && j < it.nt; ++j) {
-          if (j < it.nt_a) {
-            if (j == 0) // O_A still holds the previous item until its epilogue has read it
-              ok = mbar_wait(bar(BAR_OFREE + 0), (n_it & 1) ^ 1, abort_flag, p.error_flag, 11);
-            if (ok) ok = issue_pv(0, kv + j, j == 0, !has_b);
-            if (ok && j + 1 < it.nt_a) {
-              ok = issue_qk(0, kv + j + 1, !has_b);
-              if (ok && !has_b && j + 2 == it.nt_a) tc_commit(bar(BAR_QEMPTY));
-            }
-          }
-          if (ok && has_b) {
-            if (j == 0) ok = mbar_wait(bar(BAR_OFREE + 1), (n_it & 1) ^ 1, abort_flag, p.error_flag, 12);
-            if (ok) ok = issue_pv(1, kv + j, j == 0, true);
-            if (ok && j + 1 < it.nt_b) {
-              ok = issue_qk(1, kv + j + 1, true);
-              if (ok && j + 2 == it.nt_b) tc_commit(bar(BAR_QEMPTY)); // last Q.K^T of the item
-            }
-          }
-        }
-        kv += it.nt;
       }
     }
   } else {
@@ -398,117 +335,108 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // ------------------------------------------------------------ softmax + epilogue of tile X
     const int x = (warp >> 2) - 1;               // 0: tile A (warps 4-7), 1: tile B (warps 8-11)
     const int quad = warp & 3;                   // TMEM lane quadrant this warp may touch
+    const int trow0 = row0 + x * kBM;
+    const int row = trow0 + quad * 32 + lane;    // query token index within the call
+    const int ntx = x == 0 ? nt_a : nt_b;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t scol = tmem + lane_addr + kColS + 128 * x;
     const uint32_t ocol = tmem + lane_addr + kColO + 128 * x;
-    uint32_t nt_done = 0;                        // tiles processed so far across items (barrier phases)
+    const int vis_end = min(p.n, p.offset + row + 1); // columns < vis_end are visible to this row
+    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < n_items; w += gridDim.x) {
-      const Item it = make_item(p, w);
-      const int trow0 = it.row0 + x * kBM;
-      const int row = trow0 + quad * 32 + lane;    // query token index within the call
-      const int ntx = x == 0 ? it.nt_a : it.nt_b;
-      const int vis_end = min(p.n, p.offset + row + 1); // columns < vis_end are visible to this row
-      float m_ref = -INFINITY, l = 0.f;
-      for (int j = 0; j < ntx; ++j, ++nt_done) {
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + x), nt_done & 1, abort_flag, p.error_flag, 7))) {
+    for (int j = 0; j < ntx; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + x), j & 1, abort_flag, p.error_flag, 7))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t su[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld32(scol + 32 * c, su + 32 * c);
+      tc_wait_ld();
+      const int col0 = j * kBN;
+      // only the last tiles of a row block cross the diagonal or the end of the cache
+      if (col0 + kBN > min(p.n, p.offset + trow0 + 1)) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (col0 + c >= vis_end) su[c] = 0xff800000u; // -inf
+      }
+      // row max with eight independent chains
+      float mxa[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mxa[i] = __uint_as_float(su[i]);
+#pragma unroll
+      for (int c = 8; c < 128; c += 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mxa[i] = fmaxf(mxa[i], __uint_as_float(su[c + i]));
+      }
+      float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                       fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+      mx *= p.scale_log2;
+      // lazy rescale: keep the old reference max unless the new one is much larger
+      const bool grow = mx > m_ref + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow) && j > 0) {
+        // O must hold every P.V issued so far before it is rescaled
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + x), (j - 1) & 1, abort_flag, p.error_flag, 8))) {
           ok = false;
           break;
         }
         tc_fence_after();
-        uint32_t su[128];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tc_ld32(scol + 32 * c, su + 32 * c);
-        tc_wait_ld();
-        const int col0 = j * kBN;
-        // only the last tiles of a row block cross the diagonal or the end of the cache
-        if (col0 + kBN > min(p.n, p.offset + trow0 + 1)) {
-#pragma unroll
-          for (int c = 0; c < 128; ++c)
-            if (col0 + c >= vis_end) su[c] = 0xff800000u; // -inf
-        }
-        // row max with eight independent chains
-        float mxa[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) mxa[i] = __uint_as_float(su[i]);
-#pragma unroll
-        for (int c = 8; c < 128; c += 8) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) mxa[i] = fmaxf(mxa[i], __uint_as_float(su[c + i]));
-        }
-        float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                         fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
-        mx *= p.scale_log2;
-        // lazy rescale: keep the old reference max unless the new one is much larger
-        const bool grow = mx > m_ref + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, grow) && j > 0) {
-          // O must hold every P.V issued so far before it is rescaled
-          if (!__all_sync(0xffffffffu,
-                          mbar_wait(bar(BAR_ODONE + x), (nt_done - 1) & 1, abort_flag, p.error_flag, 8))) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const float f = grow ? ex2(m_ref - mx) : 1.f;
-          l *= f;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tc_ld32(ocol + 32 * c, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tc_st32(ocol + 32 * c, o);
-          }
-          tc_wait_st();
-        }
-        if (grow) m_ref = mx;
-        // P = 2^(s*scale - m_ref), packed pairs written back to TMEM half a tile at a time
-        uint32_t pk[64];
-        float sums[4] = {0.f, 0.f, 0.f, 0.f};
-        const float neg_m = -m_ref;
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float p0 = ex2(fmaf(__uint_as_float(su[2 * c]), p.scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(su[2 * c + 1]), p.scale_log2, neg_m));
-          sums[c & 3] += p0 + p1;
-          pk[c] = Elem<T>::pack(p0, p1);
-          if (c == 31) tc_st32(scol, pk);
-        }
-        l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-        tc_st32(scol + 32, pk + 32);
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar(BAR_PREADY + x));
-      }
-      if (!ok) break;
-      if (ntx > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + x), (nt_done - 1) & 1, abort_flag, p.error_flag, 9));
-        if (!ok) break;
-        tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        T *dst = static_cast<T *>(p.out) + it.b * p.out_seq + static_cast<long>(row) * p.out_tok + it.h * kHeadDim;
+        const float f = grow ? ex2(m_ref - mx) : 1.f;
+        l *= f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
           tc_ld32(ocol + 32 * c, o);
           tc_wait_ld();
-          if (row < p.m) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 u;
-              u.x = Elem<T>::pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-              u.y = Elem<T>::pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-              u.z = Elem<T>::pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-              u.w = Elem<T>::pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-              *reinterpret_cast<uint4 *>(dst + 32 * c + i) = u;
-            }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tc_st32(ocol + 32 * c, o);
+        }
+        tc_wait_st();
+      }
+      if (grow) m_ref = mx;
+      // P = 2^(s*scale - m_ref), packed pairs written back to TMEM half a tile at a time
+      uint32_t pk[64];
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_ref;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = ex2(fmaf(__uint_as_float(su[2 * c]), p.scale_log2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(su[2 * c + 1]), p.scale_log2, neg_m));
+        sums[c & 3] += p0 + p1;
+        pk[c] = Elem<T>::pack(p0, p1);
+        if (c == 31) tc_st32(scol, pk);
+      }
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      tc_st32(scol + 32, pk + 32);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_PREADY + x));
+    }
+    if (ok && ntx > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + x), (ntx - 1) & 1, abort_flag, p.error_flag, 9));
+    if (ok && ntx > 0) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T *dst = static_cast<T *>(p.out) + b * p.out_seq + static_cast<long>(row) * p.out_tok + h * kHeadDim;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tc_ld32(ocol + 32 * c, o);
+        tc_wait_ld();
+        if (row < p.m) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 u;
+            u.x = Elem<T>::pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            u.y = Elem<T>::pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            u.z = Elem<T>::pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            u.w = Elem<T>::pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4 *>(dst + 32 * c + i) = u;
           }
         }
       }
-      // O_X has been read: the next item's first P.V may overwrite it
-      tc_fence_before();
-      mbar_arrive(bar(BAR_OFREE + x));
     }
   }
   tc_fence_before();
@@ -604,18 +532,7 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   kp.out_tok = g.out_tok;
   kp.scale_log2 = p.scale_log2;
   kp.error_flag = err_dev;
-  kp.n_heads = g.n_heads;
-  kp.batch = g.batch;
-  kp.n_qblocks = (p.m + 2 * kBM - 1) / (2 * kBM);
-  const long n_items = static_cast<long>(kp.n_qblocks) * g.n_heads * g.batch;
-  if (n_items > 0x7fffffffL) return cudaErrorNotSupported;
-  static int sm_count[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
-    cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-  const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
-  dim3 grid(static_cast<unsigned>(n_items < sms ? n_items : sms)); // persistent: one CTA per SM
+  dim3 grid((p.m + 2 * kBM - 1) / (2 * kBM), g.n_heads, g.batch);
   cudaError_t e;
   if (bf16) {
     e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
