@@ -67,8 +67,10 @@ int gpu_attention_layer_decode_ragged(void *layer, void *out, const void *q, con
                                       gpu_stream_t stream);
 
 /* Cache lengths that a model uploads once per step for all its layers: device
- * int32 [batch] and max(kv_len) + 1.  While set, decode calls use it. */
-int gpu_attention_layer_set_shared_lens(void *layer, const int32_t *kv_len_dev, int max_kv_len);
+ * int32 [batch], max(kv_len) + 1, and sum(kv_len + 1) (scheduling hint, 0 =
+ * unknown).  While set, decode calls use it. */
+int gpu_attention_layer_set_shared_lens(void *layer, const int32_t *kv_len_dev, int max_kv_len,
+                                        long total_kv_len);
 
 /* The same forward with HOST buffers: qkv_host [batch][cur_size][(n_heads +
  * 2 n_kv_heads)*D] (q, k, v columns of one packed projection row; pinned memory

@@ -116,6 +116,9 @@ typedef struct gpu_attn_desc {
   int64_t kv_in_seq_stride, kv_in_tok_stride;
   int64_t out_seq_stride, out_tok_stride;
   int64_t cache_seq_stride, cache_head_stride, cache_pos_stride;
+  int64_t total_kv_len;  /* scheduling hint for gpu_attn_decode_layer: sum over the batch of the cache
+                            positions the call reads per KV head (kv_len[b] + append_new); 0 = unknown.
+                            Only the split size depends on it, never the result's meaning. */
 } gpu_attn_desc;
 
 /* RoPE(Q) -> q_out, RoPE(K) -> k_cache, V -> v_cache for m new tokens of every

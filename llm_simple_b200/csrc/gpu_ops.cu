@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <mutex>
 #include <string>
+#include <cstdlib>
 
 using namespace b200attn;
 
@@ -84,17 +85,34 @@ float scale_log2_of(int head_dim) {
   return (1.0f / sqrtf(static_cast<float>(head_dim))) * 1.4426950408889634f;
 }
 
-// Positions per split: enough CTAs to fill 148 SMs x 2 resident CTAs several
-// times over, but no split shorter than 256 positions (128 KB of K+V).
-int pick_chunk(int units, int max_len) {
-  int forced = g_decode_chunk.load();
+// Positions per split of the decode kernel.  total_len is the number of cache
+// positions the call reads per KV head, summed over the batch (<= 0: unknown,
+// taken as 5/8 of batch * max_len).  Two regimes, both measured on B200 with
+// 148 SMs x 2 resident CTAs = 296 slots:
+//   - the work fits one wave: the smallest split for which the expected CTA
+//     count (full splits plus about half a ragged split per sequence and head)
+//     stays within the slots -- no CTA waits for a slot and the merge stays small;
+//   - otherwise about 1024 positions (512 KB of K+V) per CTA: per-CTA set-up and
+//     pipeline fill cost about 3 us, so shorter splits lose more than they balance.
+constexpr int kMinChunk = 256;
+int pick_chunk(int batch, int kv_heads, long total_len, int max_len) {
+  const int forced = g_decode_chunk.load();
   if (forced > 0) return forced;
-  const long want_ctas = 148L * 2 * 8;
-  long per_unit = (want_ctas + units - 1) / units;
-  if (per_unit < 1) per_unit = 1;
-  long chunk = (max_len + per_unit - 1) / per_unit;
+  const long slots = 296, fill = 272; // resident CTAs, and how many of them to aim for
+  const long units = static_cast<long>(batch) * kv_heads;
+  if (total_len <= 0) total_len = static_cast<long>(batch) * max_len * 5 / 8;
+  const long positions = total_len * kv_heads; // over all (sequence, KV head) pairs
+  long chunk = 1024;
+  if (units / 2 < fill) {
+    const long single = (positions + (fill - units / 2) - 1) / (fill - units / 2);
+    if (single <= 1536 || units <= slots) chunk = single;
+    // nearly whole sequences: do not split at all (no partials, no merge launch)
+    if (units <= slots && single * 4 >= static_cast<long>(max_len) * 3) chunk = max_len;
+  }
   chunk = ((chunk + 63) / 64) * 64;
-  if (chunk < 256) chunk = 256;
+  if (chunk < kMinChunk) chunk = kMinChunk;
+  const long cap = ((static_cast<long>(max_len) + 63) / 64) * 64;
+  if (chunk > cap) chunk = cap;
   return static_cast<int>(chunk);
 }
 
@@ -163,7 +181,7 @@ int ref_attention(void *out, const void *q, const void *k, const void *v, int m,
     {
       std::lock_guard<std::mutex> lk(g_ws_mutex);
       if (dev >= 0 && dev < 64 && g_ws[dev].ptr) {
-        const int chunk = pick_chunk(kv_heads, n);
+        const int chunk = pick_chunk(1, kv_heads, n, n);
         const int splits = (n + chunk - 1) / chunk;
         const long rows = static_cast<long>(m) * g.n_heads;
         if (splits > 1 && decode_ws_bytes(rows, splits) <= g_ws[dev].bytes) {
@@ -346,7 +364,9 @@ int gpu_attn_prefill_layer(const gpu_attn_desc *desc, void *out, const void *q, 
 
 size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len) {
   if (!desc || desc->batch <= 0 || desc->n_kv_heads <= 0 || max_kv_len <= 0) return 0;
-  const int chunk = pick_chunk(desc->batch * desc->n_kv_heads, max_kv_len);
+  // enough for the shortest split the call may choose, whatever length hint it is given
+  const int forced = g_decode_chunk.load();
+  const int chunk = forced > 0 ? forced : kMinChunk;
   const int splits = (max_kv_len + chunk - 1) / chunk;
   return decode_ws_bytes(static_cast<long>(desc->batch) * desc->n_heads, splits);
 }
@@ -388,9 +408,9 @@ int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial
   p.append = append_new ? 1 : 0;
   p.rotate_q = 1;
   p.is_neox = desc->is_neox_style ? 1 : 0;
-  p.chunk = pick_chunk(desc->batch * desc->n_kv_heads, max_kv_len);
-  p.max_splits = (max_kv_len + p.chunk - 1) / p.chunk;
   p.scale_log2 = scale_log2_of(desc->head_dim);
+  p.chunk = pick_chunk(desc->batch, desc->n_kv_heads, desc->total_kv_len, max_kv_len);
+  p.max_splits = (max_kv_len + p.chunk - 1) / p.chunk;
   if (p.max_splits > 1) {
     const long rows = static_cast<long>(desc->batch) * desc->n_heads;
     const size_t need = decode_ws_bytes(rows, p.max_splits);

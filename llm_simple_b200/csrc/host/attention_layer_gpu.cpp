@@ -133,6 +133,12 @@ gpu_attn_desc AttentionLayerGPUImpl::MakeDesc(int batch, int m, long q_tok, long
   return d;
 }
 
+static long sum_lens(const int32_t *lens, int batch) {
+  long s = 0;
+  for (int b = 0; b < batch; ++b) s += lens[b] + 1;
+  return s;
+}
+
 int AttentionLayerGPUImpl::UploadLens(const int32_t *lens, int batch, cudaStream_t stream) {
   // the pinned staging array is reused by every call: wait until the previous upload has been read
   cudaError_t e = cudaStreamSynchronize(stream);
@@ -172,6 +178,7 @@ int AttentionLayerGPUImpl::DecodeRagged(void *out, const void *q, const void *k,
   if (batch <= 0 || batch > cfg_.max_batch) return GPU_OPS_E_INVALID;
   if (shared_lens_) {
     gpu_attn_desc d = MakeDesc(batch, 1, 0, 0, 0, 0);
+    d.total_kv_len = shared_total_;
     return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_, shared_lens_,
                                  nullptr, 1, shared_max_len_, workspace_->data_ptr, workspace_bytes_, stream);
   }
@@ -184,6 +191,7 @@ int AttentionLayerGPUImpl::DecodeRagged(void *out, const void *q, const void *k,
   int rc = UploadLens(kv_len_host, batch, stream);
   if (rc) return rc;
   gpu_attn_desc d = MakeDesc(batch, 1, 0, 0, 0, 0);
+  d.total_kv_len = sum_lens(kv_len_host, batch);
   return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_,
                                static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
                                workspace_->data_ptr, workspace_bytes_, stream);
@@ -221,6 +229,7 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
   int rc;
   if (ctx.cur_size == 1 && shared_lens_) {
     gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
+    d.total_kv_len = shared_total_;
     rc = gpu_attn_decode_layer(&d, staging_out_->data_ptr, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_,
                                freq_cis_, shared_lens_, nullptr, 1, shared_max_len_, workspace_->data_ptr,
                                workspace_bytes_, s);
@@ -238,6 +247,7 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
     if ((rc = UploadLens(kv_len_host, batch, s))) return rc;
     // q, k, v are columns of one packed row: strides say so
     gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
+    d.total_kv_len = sum_lens(kv_len_host, batch);
     rc = gpu_attn_decode_layer(&d, staging_out_->data_ptr, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_,
                                freq_cis_, static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
                                workspace_->data_ptr, workspace_bytes_, s);

@@ -87,9 +87,11 @@ public:
   // lengths (tokens already cached per sequence) and its maximum + 1.  While
   // set, decode calls use it instead of uploading their own copy (one upload per
   // step by the model instead of one per layer).  NULL unsets.
-  void SetSharedLens(const int32_t *kv_len_dev, int max_kv_len) {
+  // total_kv_len: sum over the batch of kv_len + 1 (scheduling hint; 0 = unknown).
+  void SetSharedLens(const int32_t *kv_len_dev, int max_kv_len, long total_kv_len = 0) {
     shared_lens_ = kv_len_dev;
     shared_max_len_ = max_kv_len;
+    shared_total_ = total_kv_len;
   }
 
   const AttentionConfig &config() const { return cfg_; }
@@ -116,6 +118,7 @@ protected:
   size_t staging_in_bytes_{0}, staging_out_bytes_{0};
   const int32_t *shared_lens_{nullptr};
   int shared_max_len_{0};
+  long shared_total_{0};
 };
 
 // Llama-2 flavour: MHA, fp16 (the reference forces DT_FLOAT16 for llama2,

@@ -80,9 +80,9 @@ int gpu_attention_layer_decode_ragged(void *layer, void *out, const void *q, con
   return as_layer(layer)->DecodeRagged(out, q, k, v, kv_len_host, batch, static_cast<cudaStream_t>(stream));
 }
 
-int gpu_attention_layer_set_shared_lens(void *layer, const int32_t *kv_len_dev, int max_kv_len) {
+int gpu_attention_layer_set_shared_lens(void *layer, const int32_t *kv_len_dev, int max_kv_len, long total_kv_len) {
   if (!layer || (kv_len_dev && max_kv_len <= 0)) return GPU_OPS_E_INVALID;
-  as_layer(layer)->SetSharedLens(kv_len_dev, max_kv_len);
+  as_layer(layer)->SetSharedLens(kv_len_dev, max_kv_len, total_kv_len);
   return GPU_OPS_OK;
 }
 

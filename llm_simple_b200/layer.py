@@ -37,7 +37,7 @@ def lib():
         L.gpu_attention_layer_destroy.argtypes = [vp]
         L.gpu_attention_layer_forward.argtypes = [vp] * 5 + [i, i, i, vp]
         L.gpu_attention_layer_decode_ragged.argtypes = [vp] * 6 + [i, vp]
-        L.gpu_attention_layer_set_shared_lens.argtypes = [vp, vp, i]
+        L.gpu_attention_layer_set_shared_lens.argtypes = [vp, vp, i, ctypes.c_long]
         L.gpu_attention_layer_forward_host.argtypes = [vp, vp, vp, i, i, i, vp, vp]
         L.gpu_attention_layer_cache.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
         _ready = True
@@ -91,8 +91,9 @@ class AttentionLayer:
                                                            ops._ptr(v), lens.ctypes.data, len(lens),
                                                            ops._stream(stream)))
 
-    def set_shared_lens(self, kv_len_dev, max_kv_len):
-        ops._check(lib().gpu_attention_layer_set_shared_lens(self.h, ops._ptr(kv_len_dev), max_kv_len))
+    def set_shared_lens(self, kv_len_dev, max_kv_len, total_kv_len=0):
+        ops._check(lib().gpu_attention_layer_set_shared_lens(self.h, ops._ptr(kv_len_dev), max_kv_len,
+                                                             total_kv_len))
 
     def forward_host(self, out_host, qkv_host, batch, cur_pos, prev_pos, kv_len=None, stream=None):
         lens_ptr = None

@@ -39,7 +39,7 @@ class AttnDesc(ctypes.Structure):
         ("kv_in_seq_stride", ctypes.c_int64), ("kv_in_tok_stride", ctypes.c_int64),
         ("out_seq_stride", ctypes.c_int64), ("out_tok_stride", ctypes.c_int64),
         ("cache_seq_stride", ctypes.c_int64), ("cache_head_stride", ctypes.c_int64),
-        ("cache_pos_stride", ctypes.c_int64),
+        ("cache_pos_stride", ctypes.c_int64), ("total_kv_len", ctypes.c_int64),
     ]
 
 

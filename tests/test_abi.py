@@ -34,8 +34,8 @@ def test_library_exports_every_symbol_of_the_host_layer_header():
 
 def test_descriptor_struct_matches_the_header_layout():
     from llm_simple_b200 import ops
-    # 6 x int32 then 9 x int64, no padding
-    assert ctypes.sizeof(ops.AttnDesc) == 6 * 4 + 9 * 8
+    # 6 x int32 then 10 x int64, no padding
+    assert ctypes.sizeof(ops.AttnDesc) == 6 * 4 + 10 * 8
     assert ops.AttnDesc.q_seq_stride.offset == 24
     d = ops.make_desc(ops.DT_BFLOAT16, 2, 40, 8, 1, 4096, layout="head")
     assert (d.cache_head_stride, d.cache_pos_stride, d.cache_seq_stride) == (4096 * 128, 128, 8 * 4096 * 128)

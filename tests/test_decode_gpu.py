@@ -165,7 +165,7 @@ def test_empty_slice_gives_minus_inf_lse_and_is_ignored_by_the_merge(ops):
     o = torch.full((2, H, D), 7.0, dtype=torch.float32, device="cuda")
     lse = torch.zeros((2, H), dtype=torch.float32, device="cuda")
     zero = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(ops.gpu_attn_decode_workspace_bytes(desc, 1), dtype=torch.uint8, device="cuda")
     ops.gpu_attn_decode_layer(desc, None, o[0], lse[0], q, None, None, kc, kc, table, zero, zero, False, 1, ws,
                               ws.numel())
     torch.cuda.synchronize()

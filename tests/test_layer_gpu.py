@@ -115,13 +115,18 @@ def test_host_buffer_prefill_matches_device_prefill(layer):
 
 
 def test_pooled_temporaries_are_recycled(layer):
-    """q_emb and the output tensor come from GPUAllocator and return to its pool."""
+    """A freed device block goes back to GPUAllocator's pool and serves the next request of that size."""
     L = layer.lib()
-    p1 = L.gpu_allocator_allocate(1 << 20)
+    L.gpu_allocator_trim()                     # start from an empty pool on this device
+    size = 3 << 20
+    p1 = L.gpu_allocator_allocate(size)
+    assert p1
     L.gpu_allocator_deallocate(p1)
     before = layer.allocator_stats()
-    p2 = L.gpu_allocator_allocate(1 << 20)
+    p2 = L.gpu_allocator_allocate(size)
     after = layer.allocator_stats()
     assert p2 == p1 and after["pool_hits"] == before["pool_hits"] + 1
     assert after["backend_allocs"] == before["backend_allocs"]
     L.gpu_allocator_deallocate(p2)
+    L.gpu_allocator_trim()
+    assert layer.allocator_stats()["pooled_bytes"] == 0
