@@ -42,6 +42,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
   T *vnew_s = knew_s + kHeadDim;
   unsigned char *stage_s = smem + kDecodeQBytes + 2 * kRowBytes;
 
+  // Launched with programmatic stream serialisation: this grid may be scheduled while
+  // the previous kernel of the stream is still draining.  Let the next one in as early
+  // as possible, and touch no memory before the previous grid has completed and flushed.
+  cudaTriggerProgrammaticLaunchCompletion();
+  cudaGridDependencySynchronize();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.g.group;
@@ -232,6 +237,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
 
 // grid: rows; block: 128 threads (one per output column)
 template <typename T> __global__ void __launch_bounds__(128) attn_merge_kernel(MergeParams p) {
+  cudaTriggerProgrammaticLaunchCompletion();
+  cudaGridDependencySynchronize(); // the partials come from the previous kernel of the stream
   const int row = blockIdx.x, d = threadIdx.x;
   const int b = row / p.rows_per_seq;
   int n_parts = p.n_parts;
@@ -374,17 +381,38 @@ template <typename K> static cudaError_t set_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
+// Launch with programmatic stream serialisation (programmatic dependent launch): the
+// grid's CTAs may be placed on SMs as the previous kernel's CTAs retire, instead of
+// after its last one has gone; the kernels order themselves with
+// cudaGridDependencySynchronize().  Hides the launch and scheduling latency between
+// the decode kernel, its merge and the next layer's decode kernel.
+template <typename P>
+static cudaError_t launch_pdl(void (*kernel)(P), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const P &p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t stream, int *launches) {
   static_assert(4 * 16 * kRedStride * 4 + 4 * 16 * 2 * 4 <= kDecodeStages * 2 * kTileBytes, "reduction buffer");
   cudaError_t e;
   dim3 grid(p.max_splits, p.g.n_kv_heads, p.g.batch);
   if (bf16) {
     if ((e = set_smem(attn_decode_kernel<__nv_bfloat16>, kDecodeSmem)) != cudaSuccess) return e;
-    attn_decode_kernel<__nv_bfloat16><<<grid, kDecodeThreads, kDecodeSmem, stream>>>(p);
+    e = launch_pdl(attn_decode_kernel<__nv_bfloat16>, grid, dim3(kDecodeThreads), kDecodeSmem, stream, p);
   } else {
     if ((e = set_smem(attn_decode_kernel<__half>, kDecodeSmem)) != cudaSuccess) return e;
-    attn_decode_kernel<__half><<<grid, kDecodeThreads, kDecodeSmem, stream>>>(p);
+    e = launch_pdl(attn_decode_kernel<__half>, grid, dim3(kDecodeThreads), kDecodeSmem, stream, p);
   }
+  if (e != cudaSuccess) return e;
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   *launches = 1;
   if (p.max_splits > 1) {
@@ -416,10 +444,9 @@ cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t st
 
 cudaError_t launch_attn_merge(const MergeParams &p, bool bf16, cudaStream_t stream) {
   if (p.rows <= 0) return cudaSuccess;
-  if (bf16)
-    attn_merge_kernel<__nv_bfloat16><<<p.rows, 128, 0, stream>>>(p);
-  else
-    attn_merge_kernel<__half><<<p.rows, 128, 0, stream>>>(p);
+  cudaError_t e = bf16 ? launch_pdl(attn_merge_kernel<__nv_bfloat16>, dim3(p.rows), dim3(128), 0, stream, p)
+                       : launch_pdl(attn_merge_kernel<__half>, dim3(p.rows), dim3(128), 0, stream, p);
+  if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
 

@@ -98,7 +98,7 @@ constexpr int kMinChunk = 256;
 int pick_chunk(int batch, int kv_heads, long total_len, int max_len) {
   const int forced = g_decode_chunk.load();
   if (forced > 0) return forced;
-  const long slots = 296, fill = 272; // resident CTAs, and how many of them to aim for
+  const long slots = 296, fill = 256; // resident CTAs, and how many of them to aim for
   const long units = static_cast<long>(batch) * kv_heads;
   if (total_len <= 0) total_len = static_cast<long>(batch) * max_len * 5 / 8;
   const long positions = total_len * kv_heads; // over all (sequence, KV head) pairs
