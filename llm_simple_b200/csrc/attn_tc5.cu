@@ -13,7 +13,8 @@
 //                 TMEM and V from shared memory (N-major operand); per KV tile
 //                 it issues  P.V(A) Q.K(A,next)  P.V(B) Q.K(B,next), so that the
 //                 tensor pipe works for one query tile while the other one's
-//                 softmax runs
+//                 softmax runs; the first half of each P.V starts as soon as the
+//                 first 64 positions of P are published
 //   warps 2-3     idle (they only give their registers away)
 //   warps 4-7     softmax of tile A, warps 8-11 softmax of tile B: one thread
 //                 per query row (TMEM lane): tcgen05.ld of the S row, running
@@ -58,7 +59,7 @@ constexpr float kRescaleThreshold = 8.0f;        // log2 domain
 
 // barrier slots (8 bytes each) inside the barrier block; X = 0 (tile A) or 1 (tile B)
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_COUNT = 15 };
+       BAR_ODONE = 13, BAR_PHALF = 15, BAR_COUNT = 17 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -166,6 +167,32 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Two fp32 values in one 64-bit register, for the packed fp32x2 arithmetic of sm_100:
+// one instruction scales (or sums) two scores.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1, as two words.
 //   K-major operand  ([rows][64 elem] half tiles): LBO field 1 (unused), SBO = 1024 B (8 rows)
 //   MN-major operand (V: [pos][64 elem] half tiles): LBO = distance between the two 64-element
@@ -233,6 +260,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar(BAR_SFULL + s), 1);
       mbar_init(bar(BAR_PREADY + s), 128);
       mbar_init(bar(BAR_ODONE + s), 1);
+      mbar_init(bar(BAR_PHALF + s), 128);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -301,17 +329,23 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       // O_X += P_X . V[j] ; `last` marks the last reader of V[j]
       auto issue_pv = [&](int x, int j, bool last) -> bool {
         const int s = j % kStages;
-        if (!mbar_wait(bar(BAR_PREADY + x), j & 1, abort_flag, p.error_flag, 5)) return false;
+        // The softmax warps publish the first 64 positions of P before they start on the
+        // other 64, so that half of this product overlaps their remaining exponentials.
+        if (!mbar_wait(bar(BAR_PHALF + x), j & 1, abort_flag, p.error_flag, 10)) return false;
         if (!mbar_wait(bar(BAR_VFULL + s), (j / kStages) & 1, abort_flag, p.error_flag, 6)) return false;
         tc_fence_after();
         const uint32_t pcol = tmem + kColS + 128 * x, ocol = tmem + kColO + 128 * x;
         const uint32_t dv = dv0 + s * kTileStep;
         const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 4; ++k) {
           // 16 positions per step: 8 TMEM columns of packed P, 16 rows (2048 B) of V
           tc_mma_ts(ocol, pcol + 8 * k, dv + k * (2048 >> 4), kDescHi, idesc_pv, k > 0 ? 1u : acc0);
         }
+        if (!mbar_wait(bar(BAR_PREADY + x), j & 1, abort_flag, p.error_flag, 5)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 4; k < 8; ++k) tc_mma_ts(ocol, pcol + 8 * k, dv + k * (2048 >> 4), kDescHi, idesc_pv, 1u);
         if (last) tc_commit(bar(BAR_VEMPTY + s));
         tc_commit(bar(BAR_ODONE + x));
         return true;
@@ -361,17 +395,16 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int c = 0; c < 128; ++c)
           if (col0 + c >= vis_end) su[c] = 0xff800000u; // -inf
       }
-      // row max with eight independent chains
+      // row max with eight independent chains of three-input maxima
       float mxa[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mxa[i] = __uint_as_float(su[i]);
+      for (int i = 0; i < 8; ++i) mxa[i] = fmaxf(__uint_as_float(su[i]), __uint_as_float(su[8 + i]));
 #pragma unroll
-      for (int c = 8; c < 128; c += 8) {
+      for (int c = 16; c < 128; c += 16) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) mxa[i] = fmaxf(mxa[i], __uint_as_float(su[c + i]));
+        for (int i = 0; i < 8; ++i) mxa[i] = max3(mxa[i], __uint_as_float(su[c + i]), __uint_as_float(su[c + 8 + i]));
       }
-      float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                       fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+      float mx = fmaxf(max3(mxa[0], mxa[1], mxa[2]), fmaxf(max3(mxa[3], mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
       mx *= p.scale_log2;
       // lazy rescale: keep the old reference max unless the new one is much larger
       const bool grow = mx > m_ref + kRescaleThreshold;
@@ -398,17 +431,30 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (grow) m_ref = mx;
       // P = 2^(s*scale - m_ref), packed pairs written back to TMEM half a tile at a time
       uint32_t pk[64];
-      float sums[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_ref;
+      uint64_t sums[2] = {0ull, 0ull};            // two fp32x2 accumulators
+      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_ref, -m_ref);
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        const float p0 = ex2(fmaf(__uint_as_float(su[2 * c]), p.scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(su[2 * c + 1]), p.scale_log2, neg_m));
-        sums[c & 3] += p0 + p1;
+        const uint64_t x2 = fma2(pack2(__uint_as_float(su[2 * c]), __uint_as_float(su[2 * c + 1])), scale2, neg_m2);
+        float x0, x1;
+        unpack2(x2, x0, x1);
+        const float p0 = ex2(x0), p1 = ex2(x1);
+        sums[c & 1] = add2(sums[c & 1], pack2(p0, p1));
         pk[c] = Elem<T>::pack(p0, p1);
-        if (c == 31) tc_st32(scol, pk);
+        if (c == 31) {
+          // first 64 positions of P: the MMA warp may start P.V on them
+          tc_st32(scol, pk);
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(BAR_PHALF + x));
+        }
       }
-      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      {
+        float a0, a1, a2, a3;
+        unpack2(sums[0], a0, a1);
+        unpack2(sums[1], a2, a3);
+        l += (a0 + a1) + (a2 + a3);
+      }
       tc_st32(scol + 32, pk + 32);
       tc_wait_st();
       tc_fence_before();
