@@ -43,6 +43,9 @@ DT_FP16, DT_BF16 = 4, 5
 
 CFG4 = dict(name="cfg4 Qwen2.5-14B-shaped batched GQA decode", layers=48, batch=64, n_heads=40, n_kv_heads=8,
             len_lo=1024, len_hi=4096, theta=1e6, neox=True, seed=20254)
+# dram__bytes_read.sum + dram__bytes_write.sum of attn_decode_kernel over its algorithmic bytes,
+# from the ncu capture summarised in profiles/attn_decode_kernel_cfg4_1layer.md (700.9 / 693.68 MB)
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 700.9 / 693.68
 CFG3 = dict(name="cfg3 Llama-2-13B-shaped causal prefill", batch=8, seq=2048, n_heads=40, theta=1e4, neox=False)
 
 
@@ -317,8 +320,14 @@ def main():
     value = bytes_layer_all * layers / (ms_per_step * 1e-3) / 1e9
     layer_ms = ms_per_step / layers
     achieved = bytes_layer_rank / (layer_ms * 1e-3) / 1e9
+    # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
+    # workload's own one-layer launch at N = 1 (700.9 MB against 693.68 MB algorithmic, profiles/);
+    # a shard of the same launch is scaled by the bytes it processes (traffic is all K/V streaming).
+    traffic = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_layer_rank
     roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"], "traffic": None, "peak_source": pk["source"],
+                "frac": achieved / pk["hbm"], "traffic": traffic,
+                "traffic_source": "ncu capture of the one-layer launch, scaled by algorithmic bytes",
+                "peak_source": pk["source"],
                 "kernel": "attn_decode_kernel (+ attn_merge_kernel, one launch pair per layer)",
                 "launch_ms": layer_ms, "algorithmic_bytes_per_launch": bytes_layer_rank,
                 "frac_of_nominal_8TBs": achieved / 8000.0}
@@ -468,6 +477,33 @@ def prefill_leg(torch, ops, orc, world, dev, barrier, pk):
         ms = statistics.median(times)
         fl = prefill_flops(batch, c["n_heads"], S, 0)
         res[name] = {"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12, "ms_min": min(times)}
+    # The RoPE + append pass on its own, fed from three tensors and from one fused q|k|v
+    # projection row with a bias row (HBM-bound: every element read once, written once).
+    row = 3 * H_l * D
+    qkv = torch.randn((batch, S, row), dtype=torch.float16, device=dev)
+    bias = torch.randn((row,), dtype=torch.float16, device=dev)
+    pass_bytes = 2 * batch * S * row * 2
+    for name in ("rope_append_pass", "qkv_fused_rope_append_pass"):
+        def run():
+            if name == "rope_append_pass":
+                ops.gpu_rope_kv_append_layer(desc, qe, kc, vc, q, k, v, table, None, 0, S, stream=stream)
+            else:
+                ops.gpu_qkv_rope_kv_append_layer(desc, qe, kc, vc, qkv, S * row, row, bias, table, None, 0, S,
+                                                 stream=stream)
+        for _ in range(3):
+            run()
+        times = []
+        for _ in range(10):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            run()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        gbs = pass_bytes / (ms * 1e-3) / 1e9
+        res[name] = {"ms": ms, "gbs": gbs, "bytes": pass_bytes, "frac_of_hbm_peak": gbs / pk["hbm"]}
     per_rank = res["attention_only"]["tflops"] / world
     res.update({"workload": c["name"], "dtype": "fp16", "flops_per_layer": prefill_flops(batch, c["n_heads"], S, 0),
                 "l2": "256 MB flush between iterations",

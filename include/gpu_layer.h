@@ -80,6 +80,15 @@ int gpu_attention_layer_forward_host(void *layer, void *out_host, const void *qk
                                      int cur_pos, int prev_pos, const int32_t *kv_len_host,
                                      gpu_stream_t stream);
 
+/* Device-buffer entry fed from a fused projection output: qkv [batch][cur_size]
+ * [(n_heads + 2 n_kv_heads)*D] on the device (the tensor npu_split_qkv_layer,
+ * prebuild/npu_ops.h:27-30, would split), qkv_bias one such row or NULL (the
+ * Qwen2 q/k/v biases, src/llama2_layer_npu.cpp:1020-1055), out [batch][cur_size]
+ * [n_heads*D] on the device.  kv_len_host as for gpu_attention_layer_forward_host. */
+int gpu_attention_layer_forward_fused(void *layer, void *out, const void *qkv, const void *qkv_bias,
+                                      int batch, int cur_pos, int prev_pos,
+                                      const int32_t *kv_len_host, gpu_stream_t stream);
+
 /* Device addresses of the layer's K and V caches. */
 int gpu_attention_layer_cache(void *layer, void **k_cache, void **v_cache);
 

@@ -92,6 +92,14 @@ int gpu_rope_single_layer(void *output_x_dev, const void *freqs_cis_dev,
                           const void *input_x_dev, int start_pos, int cur_size, int n_heads,
                           int hidden_dim, int is_neox_style, int dt, gpu_stream_t stream);
 
+/* Replaces npu_split_qkv_layer (prebuild/npu_ops.h:27-30; declared there, not
+ * called by the reference's layers): input_qkv [batch][q_dim + k_dim + v_dim]
+ * is split row by row into three dense tensors.  Each dim must be a multiple
+ * of 128 elements.  A plain copy: bit-exact. */
+int gpu_split_qkv_layer(void *output_q_dev, void *output_k_dev, void *output_v_dev,
+                        const void *input_qkv, int batch, int q_dim, int k_dim, int v_dim,
+                        int dt, gpu_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Fused operators: the same path with a batch dimension, explicit strides
  * (token-major and head-major caches) and RoPE + append in the same pass.
@@ -132,6 +140,32 @@ int gpu_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cac
                              const void *v_in, const void *freqs_cis_dev,
                              const int32_t *start_pos_dev, int start_pos, int m,
                              gpu_stream_t stream);
+
+/* The same pass fed from a FUSED projection output: each token row holds
+ * [n_heads*128 q | n_kv_heads*128 k | n_kv_heads*128 v] (row stride
+ * qkv_tok_stride >= that width, sequence stride qkv_seq_stride, in elements).
+ * qkv_bias: one row of the same width and dtype, or NULL.  With a bias every
+ * element becomes round_dtype(float(x) + float(bias)) before the rotation -- the
+ * rounding point of a projection whose epilogue adds the bias
+ * (npu_matmul_bias_nz_layer, prebuild/npu_ops.h:90-92, used by the Qwen2
+ * q/k/v projections, src/llama2_layer_npu.cpp:1020-1055, :1174-1177).
+ * Replaces npu_split_qkv_layer (prebuild/npu_ops.h:27-30) + the two RoPE calls
+ * + the two cache copies with one read of the row.  q_out is written with the
+ * descriptor's q strides; the descriptor's kv_in strides are not used. */
+int gpu_qkv_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cache,
+                                 void *v_cache, const void *qkv_in, int64_t qkv_seq_stride,
+                                 int64_t qkv_tok_stride, const void *qkv_bias,
+                                 const void *freqs_cis_dev, const int32_t *start_pos_dev,
+                                 int start_pos, int m, gpu_stream_t stream);
+
+/* output[r][c] = round_dtype(float(input[r][c]) + float(bias[c])) for rows x width
+ * elements, rows row_stride elements apart in both tensors (in place allowed);
+ * width a multiple of 128.  The bias step of gpu_qkv_rope_kv_append_layer on
+ * its own, for the one-token step, where the rotation happens inside
+ * gpu_attn_decode_layer.  No counterpart in prebuild/npu_ops.h: the reference
+ * adds the bias inside its projection (npu_matmul_bias_nz_layer, :90-92). */
+int gpu_bias_add_layer(void *output_dev, const void *input_dev, const void *bias_dev, int rows,
+                       int width, int64_t row_stride, int dt, gpu_stream_t stream);
 
 /* Causal attention of m new (already rotated) query rows per sequence over
  * cache positions [0, offset + m); row r sees positions <= offset + r.  The

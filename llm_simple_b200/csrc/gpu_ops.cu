@@ -257,6 +257,73 @@ namespace b200attn {
 void set_last_error(const char *msg) { g_last_error = msg ? msg : ""; }
 } // namespace b200attn
 
+namespace {
+
+// Sources of one RoPE + append pass: three tensors with their own strides, or three
+// column ranges of one fused projection row; bias rows are optional.
+struct RopeSources {
+  const void *q, *k, *v;
+  long q_seq, q_tok, kv_seq, kv_tok;
+  const void *bias_q, *bias_k, *bias_v;
+};
+
+int rope_append_common(const gpu_attn_desc *desc, void *q_out, void *k_cache, void *v_cache, const RopeSources &src,
+                       const void *freqs_cis_dev, const int32_t *start_pos_dev, int start_pos, int m,
+                       gpu_stream_t stream) {
+  const void *q_in = src.q, *k_in = src.k, *v_in = src.v;
+  if (!k_cache || !v_cache || !k_in || !v_in || !freqs_cis_dev || (q_out && !q_in))
+    return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (m < 0 || (!start_pos_dev && start_pos < 0)) return fail(GPU_OPS_E_INVALID, "m %d, start_pos %d", m, start_pos);
+  if (!aligned16(q_out) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(q_in) || !aligned16(k_in) ||
+      !aligned16(v_in) || !aligned16(freqs_cis_dev))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  if (m == 0) return GPU_OPS_OK;
+  RopeParams p{};
+  int slots = 0;
+  if (q_out) {
+    RopeStream &s = p.s[slots];
+    s.src = q_in;
+    s.dst = q_out;
+    s.heads = desc->n_heads;
+    s.rotate = 1;
+    s.dst_at_pos = 0;
+    s.bias = src.bias_q;
+    s.src_seq = src.q_seq;
+    s.src_tok = src.q_tok;
+    s.dst_seq = desc->q_seq_stride;
+    s.dst_tok = desc->q_tok_stride;
+    s.dst_head = 128;
+    ++slots;
+  }
+  for (int kv = 0; kv < 2; ++kv) {
+    RopeStream &s = p.s[slots++];
+    s.src = kv == 0 ? k_in : v_in;
+    s.dst = kv == 0 ? k_cache : v_cache;
+    s.heads = desc->n_kv_heads;
+    s.rotate = kv == 0 ? 1 : 0;
+    s.dst_at_pos = 1;
+    s.bias = kv == 0 ? src.bias_k : src.bias_v;
+    s.src_seq = src.kv_seq;
+    s.src_tok = src.kv_tok;
+    s.dst_seq = desc->cache_seq_stride;
+    s.dst_tok = desc->cache_pos_stride;
+    s.dst_head = desc->cache_head_stride;
+  }
+  p.slots = (q_out ? desc->n_heads : 0) + 2 * desc->n_kv_heads;
+  p.freqs_cis = static_cast<const float *>(freqs_cis_dev);
+  p.start_pos_dev = start_pos_dev;
+  p.start_pos = start_pos;
+  p.batch = desc->batch;
+  p.m = m;
+  p.is_neox = desc->is_neox_style ? 1 : 0;
+  cudaError_t e = launch_rope_append(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "rope + append launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+} // namespace
+
 extern "C" {
 
 int gpu_flash_attn_layer(void *output_dev, const void *q_dev, const void *k_dev, const void *v_dev, int m, int n,
@@ -295,49 +362,99 @@ int gpu_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cac
                              const void *k_in, const void *v_in, const void *freqs_cis_dev,
                              const int32_t *start_pos_dev, int start_pos, int m, gpu_stream_t stream) {
   if (int rc = check_desc(desc)) return rc;
-  if (!k_cache || !v_cache || !k_in || !v_in || !freqs_cis_dev || (q_out && !q_in))
-    return fail(GPU_OPS_E_INVALID, "null tensor pointer");
-  if (m < 0 || (!start_pos_dev && start_pos < 0)) return fail(GPU_OPS_E_INVALID, "m %d, start_pos %d", m, start_pos);
-  if (!aligned16(q_out) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(q_in) || !aligned16(k_in) ||
-      !aligned16(v_in) || !aligned16(freqs_cis_dev))
+  RopeSources src{q_in, k_in, v_in, desc->q_seq_stride, desc->q_tok_stride, desc->kv_in_seq_stride,
+                  desc->kv_in_tok_stride, nullptr, nullptr, nullptr};
+  return rope_append_common(desc, q_out, k_cache, v_cache, src, freqs_cis_dev, start_pos_dev, start_pos, m, stream);
+}
+
+int gpu_qkv_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cache, void *v_cache,
+                                 const void *qkv_in, int64_t qkv_seq_stride, int64_t qkv_tok_stride,
+                                 const void *qkv_bias, const void *freqs_cis_dev, const int32_t *start_pos_dev,
+                                 int start_pos, int m, gpu_stream_t stream) {
+  if (int rc = check_desc(desc)) return rc;
+  if (!qkv_in) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  const long q_dim = static_cast<long>(desc->n_heads) * 128, kv_dim = static_cast<long>(desc->n_kv_heads) * 128;
+  if (qkv_tok_stride < q_dim + 2 * kv_dim || qkv_tok_stride % 8 || qkv_seq_stride % 8 || qkv_seq_stride < 0)
+    return fail(GPU_OPS_E_INVALID, "fused row stride %lld (row holds %ld elements), sequence stride %lld",
+                static_cast<long long>(qkv_tok_stride), q_dim + 2 * kv_dim, static_cast<long long>(qkv_seq_stride));
+  if (!aligned16(qkv_in) || !aligned16(qkv_bias))
     return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
-  if (m == 0) return GPU_OPS_OK;
+  const size_t eb = 2;
+  const char *row = static_cast<const char *>(qkv_in);
+  const char *bias = static_cast<const char *>(qkv_bias);
+  RopeSources src{row,
+                  row + q_dim * eb,
+                  row + (q_dim + kv_dim) * eb,
+                  qkv_seq_stride,
+                  qkv_tok_stride,
+                  qkv_seq_stride,
+                  qkv_tok_stride,
+                  bias,
+                  bias ? bias + q_dim * eb : nullptr,
+                  bias ? bias + (q_dim + kv_dim) * eb : nullptr};
+  return rope_append_common(desc, q_out, k_cache, v_cache, src, freqs_cis_dev, start_pos_dev, start_pos, m, stream);
+}
+
+int gpu_split_qkv_layer(void *output_q_dev, void *output_k_dev, void *output_v_dev, const void *input_qkv, int batch,
+                        int q_dim, int k_dim, int v_dim, int dt, gpu_stream_t stream) {
+  if (dt != GPU_DT_FLOAT16 && dt != GPU_DT_BFLOAT16) return fail(GPU_OPS_E_UNSUPPORTED, "dtype %d", dt);
+  if (batch < 0 || q_dim < 0 || k_dim < 0 || v_dim < 0)
+    return fail(GPU_OPS_E_INVALID, "batch %d, dims %d %d %d", batch, q_dim, k_dim, v_dim);
+  if (q_dim % 128 || k_dim % 128 || v_dim % 128)
+    return fail(GPU_OPS_E_UNSUPPORTED, "dims %d %d %d: each must be a multiple of 128", q_dim, k_dim, v_dim);
+  if (batch == 0 || q_dim + k_dim + v_dim == 0) return GPU_OPS_OK; // nothing is read or written
+  if (!output_q_dev || !output_k_dev || !output_v_dev || !input_qkv)
+    return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (!aligned16(output_q_dev) || !aligned16(output_k_dev) || !aligned16(output_v_dev) || !aligned16(input_qkv))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
   RopeParams p{};
-  int slots = 0;
-  if (q_out) {
-    RopeStream &s = p.s[slots];
-    s.src = q_in;
-    s.dst = q_out;
-    s.heads = desc->n_heads;
-    s.rotate = 1;
-    s.dst_at_pos = 0;
-    s.src_seq = s.dst_seq = desc->q_seq_stride;
-    s.src_tok = s.dst_tok = desc->q_tok_stride;
-    s.dst_head = 128;
-    ++slots;
+  const long row = static_cast<long>(q_dim) + k_dim + v_dim;
+  const int dims[3] = {q_dim, k_dim, v_dim};
+  void *dsts[3] = {output_q_dev, output_k_dev, output_v_dev};
+  long col = 0;
+  for (int i = 0; i < 3; ++i) {
+    RopeStream &st = p.s[i];
+    st.src = static_cast<const char *>(input_qkv) + col * 2;
+    st.dst = dsts[i];
+    st.heads = dims[i] / 128;
+    st.src_tok = row;
+    st.dst_tok = dims[i];
+    st.dst_head = 128;
+    col += dims[i];
+    p.slots += st.heads;
   }
-  for (int kv = 0; kv < 2; ++kv) {
-    RopeStream &s = p.s[slots++];
-    s.src = kv == 0 ? k_in : v_in;
-    s.dst = kv == 0 ? k_cache : v_cache;
-    s.heads = desc->n_kv_heads;
-    s.rotate = kv == 0 ? 1 : 0;
-    s.dst_at_pos = 1;
-    s.src_seq = desc->kv_in_seq_stride;
-    s.src_tok = desc->kv_in_tok_stride;
-    s.dst_seq = desc->cache_seq_stride;
-    s.dst_tok = desc->cache_pos_stride;
-    s.dst_head = desc->cache_head_stride;
-  }
-  p.slots = (q_out ? desc->n_heads : 0) + 2 * desc->n_kv_heads;
-  p.freqs_cis = static_cast<const float *>(freqs_cis_dev);
-  p.start_pos_dev = start_pos_dev;
-  p.start_pos = start_pos;
-  p.batch = desc->batch;
-  p.m = m;
-  p.is_neox = desc->is_neox_style ? 1 : 0;
-  cudaError_t e = launch_rope_append(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(e, "rope + append launch");
+  p.batch = 1;
+  p.m = batch;
+  cudaError_t e = launch_rope_append(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "split launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+
+int gpu_bias_add_layer(void *output_dev, const void *input_dev, const void *bias_dev, int rows, int width,
+                       int64_t row_stride, int dt, gpu_stream_t stream) {
+  if (dt != GPU_DT_FLOAT16 && dt != GPU_DT_BFLOAT16) return fail(GPU_OPS_E_UNSUPPORTED, "dtype %d", dt);
+  if (rows < 0 || width < 0 || row_stride < width || row_stride % 8)
+    return fail(GPU_OPS_E_INVALID, "rows %d, width %d, row stride %lld", rows, width, static_cast<long long>(row_stride));
+  if (width % 128) return fail(GPU_OPS_E_UNSUPPORTED, "width %d: must be a multiple of 128", width);
+  if (!output_dev || !input_dev || !bias_dev) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if (!aligned16(output_dev) || !aligned16(input_dev) || !aligned16(bias_dev))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  if (rows == 0 || width == 0) return GPU_OPS_OK;
+  RopeParams p{};
+  RopeStream &st = p.s[0];
+  st.src = input_dev;
+  st.dst = output_dev;
+  st.bias = bias_dev;
+  st.heads = width / 128;
+  st.src_tok = st.dst_tok = row_stride;
+  st.dst_head = 128;
+  p.slots = st.heads;
+  p.batch = 1;
+  p.m = rows;
+  cudaError_t e = launch_rope_append(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "bias launch");
   g_launches += 1;
   return GPU_OPS_OK;
 }

@@ -206,6 +206,57 @@ std::shared_ptr<Tensor> AttentionLayerGPUImpl::Forward(std::shared_ptr<Tensor> q
   return out;
 }
 
+int AttentionLayerGPUImpl::ForwardFused(void *out, const void *qkv, const void *bias, InferenceCtx &ctx, int batch,
+                                        const int32_t *kv_len_host) {
+  if (batch <= 0 || batch > cfg_.max_batch || ctx.cur_size <= 0 || ctx.prev_pos < 0 || ctx.cur_pos > cfg_.max_seq_len)
+    return GPU_OPS_E_INVALID;
+  const long D = cfg_.head_dim;
+  const long row = (cfg_.n_heads + 2L * cfg_.n_kv_heads) * D;
+  cudaStream_t s = ctx.gpu_stream;
+  if (ctx.cur_size > 1) {
+    gpu_attn_desc d = MakeDesc(batch, ctx.cur_size, 0, 0, 0, 0);
+    auto q_emb = Tensor::MakeGPUTensor(static_cast<size_t>(batch) * ctx.cur_size * cfg_.n_heads * D, cfg_.data_type);
+    if (!q_emb->data_ptr) return GPU_OPS_E_CUDA;
+    int rc = gpu_qkv_rope_kv_append_layer(&d, q_emb->data_ptr, k_cache_raw_, v_cache_raw_, qkv, ctx.cur_size * row, row,
+                                          bias, freq_cis_, nullptr, ctx.prev_pos, ctx.cur_size, s);
+    if (rc) return rc;
+    return gpu_attn_prefill_layer(&d, out, q_emb->data_ptr, k_cache_raw_, v_cache_raw_, ctx.cur_size, ctx.prev_pos, s);
+  }
+  // one token per sequence: the decode kernel reads q, k, v as columns of the packed row
+  std::shared_ptr<Tensor> biased;
+  const char *base = static_cast<const char *>(qkv);
+  if (bias) {
+    biased = Tensor::MakeGPUTensor(static_cast<size_t>(batch) * row, cfg_.data_type);
+    if (!biased->data_ptr) return GPU_OPS_E_CUDA;
+    int rc = gpu_bias_add_layer(biased->data_ptr, qkv, bias, batch, static_cast<int>(row), row,
+                                static_cast<int>(cfg_.data_type), s);
+    if (rc) return rc;
+    base = static_cast<const char *>(biased->data_ptr);
+  }
+  const void *q = base, *k = base + cfg_.n_heads * D * 2, *v = base + (cfg_.n_heads + cfg_.n_kv_heads) * D * 2;
+  gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
+  if (shared_lens_) {
+    d.total_kv_len = shared_total_;
+    return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_, shared_lens_,
+                                 nullptr, 1, shared_max_len_, workspace_->data_ptr, workspace_bytes_, s);
+  }
+  std::vector<int32_t> uniform;
+  if (!kv_len_host) {
+    uniform.assign(batch, ctx.prev_pos);
+    kv_len_host = uniform.data();
+  }
+  int max_len = 0;
+  for (int b = 0; b < batch; ++b) {
+    if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
+    if (kv_len_host[b] + 1 > max_len) max_len = kv_len_host[b] + 1;
+  }
+  if (int rc = UploadLens(kv_len_host, batch, s)) return rc;
+  d.total_kv_len = sum_lens(kv_len_host, batch);
+  return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_,
+                               static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
+                               workspace_->data_ptr, workspace_bytes_, s);
+}
+
 int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, InferenceCtx &ctx, int batch,
                                        const int32_t *kv_len_host) {
   if (batch <= 0 || batch > cfg_.max_batch || ctx.cur_size <= 0) return GPU_OPS_E_INVALID;

@@ -78,6 +78,15 @@ public:
   int DecodeRagged(void *out, const void *q, const void *k, const void *v, const int32_t *kv_len_host, int batch,
                    cudaStream_t stream);
 
+  // Device entry fed from a fused projection output: qkv [batch][cur_size][(n_heads +
+  // 2 n_kv_heads)*D] (the tensor npu_split_qkv_layer would split), bias one such row or
+  // NULL (the q/k/v biases of the Qwen2 projections, src/llama2_layer_npu.cpp:1020-1055,
+  // when the projection itself does not add them).  Split, bias, RoPE and append happen
+  // in one pass over the row; the one-token step adds the bias in a small pass of its
+  // own and leaves the rest to the decode kernel.  kv_len_host as in ForwardHost.
+  int ForwardFused(void *out, const void *qkv, const void *bias, InferenceCtx &ctx, int batch,
+                   const int32_t *kv_len_host);
+
   // Host-buffer entry: q/k/v packed as [batch][cur_size][(n_heads + 2 n_kv_heads)*D]
   // in (pinned) host memory, output to host memory; copies are enqueued on the
   // stream around the kernels.  kv_len_host == NULL: uniform ctx.prev_pos.

@@ -94,6 +94,14 @@ int gpu_attention_layer_forward_host(void *layer, void *out_host, const void *qk
   return as_layer(layer)->ForwardHost(out_host, qkv_host, ctx, batch, kv_len_host);
 }
 
+int gpu_attention_layer_forward_fused(void *layer, void *out, const void *qkv, const void *qkv_bias, int batch,
+                                      int cur_pos, int prev_pos, const int32_t *kv_len_host, gpu_stream_t stream) {
+  if (!layer || !out || !qkv || cur_pos < prev_pos || prev_pos < 0) return GPU_OPS_E_INVALID;
+  InferenceCtx ctx(cur_pos, prev_pos);
+  ctx.gpu_stream = static_cast<cudaStream_t>(stream);
+  return as_layer(layer)->ForwardFused(out, qkv, qkv_bias, ctx, batch, kv_len_host);
+}
+
 int gpu_attention_layer_cache(void *layer, void **k_cache, void **v_cache) {
   if (!layer || !k_cache || !v_cache) return GPU_OPS_E_INVALID;
   *k_cache = as_layer(layer)->k_cache_ptr();

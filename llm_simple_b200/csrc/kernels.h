@@ -18,6 +18,7 @@ struct RopeStream {
   int heads;       // 0 disables the stream
   int rotate;      // 1: apply RoPE, 0: copy
   int dst_at_pos;  // 1: destination token index is start_pos + t (cache), 0: t
+  const void *bias; // [heads][128] of the element type added before the rotation, or null
   long src_seq, src_tok;
   long dst_seq, dst_tok, dst_head;
 };

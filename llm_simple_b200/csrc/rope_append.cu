@@ -4,7 +4,10 @@
 // cache (reference: npu_rope_layer / npu_rope_single_layer followed by two
 // device-to-device copies, src/llama2_layer_npu.cpp:206-208, :325-338,
 // :790-798, :830-843).  The same kernel serves the reference-shaped RoPE
-// operators by pointing the destinations at plain tensors.
+// operators by pointing the destinations at plain tensors, the split of a fused
+// q|k|v projection row (npu_split_qkv_layer, prebuild/npu_ops.h:27-30) by pointing
+// the three sources into that row, and the projection bias of the Qwen2 layers
+// (src/llama2_layer_npu.cpp:1020-1055) by an optional per-head bias row.
 //
 // HBM-bound: every input element is read once and every output element written
 // once with 16-byte accesses; the fp32 table row (512 B per position) is shared
@@ -13,6 +16,19 @@
 #include "common.cuh"
 
 namespace b200attn {
+
+// x + bias on one 16-byte chunk: fp32 sum of the two 16-bit values, rounded to the
+// element type (the rounding point of a projection whose epilogue adds the bias).
+template <typename T> __device__ __forceinline__ void add_bias_chunk(uint4 &u, const uint4 &bv) {
+  uint32_t *w = reinterpret_cast<uint32_t *>(&u);
+  const uint32_t *bw = reinterpret_cast<const uint32_t *>(&bv);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 x = Elem<T>::unpack(w[e]);
+    const float2 y = Elem<T>::unpack(bw[e]);
+    w[e] = Elem<T>::pack(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y));
+  }
+}
 
 // Eight threads work on one (token, head) row of 128 elements; thread i owns
 // the pairs f = 8i .. 8i+7, which live in chunks (2i, 2i+1) for the interleaved
@@ -47,6 +63,11 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeParams p) {
     const int c1 = (st.rotate && !p.is_neox) ? 2 * i + 1 : i + 8;
     uint4 u0 = *reinterpret_cast<const uint4 *>(src + c0 * 8);
     uint4 u1 = *reinterpret_cast<const uint4 *>(src + c1 * 8);
+    if (st.bias) {
+      const T *bias = static_cast<const T *>(st.bias) + slot * kHeadDim;
+      add_bias_chunk<T>(u0, *reinterpret_cast<const uint4 *>(bias + c0 * 8));
+      add_bias_chunk<T>(u1, *reinterpret_cast<const uint4 *>(bias + c1 * 8));
+    }
     if (st.rotate) {
       const float4 *tab = reinterpret_cast<const float4 *>(p.freqs_cis + (static_cast<long>(start) + t) * kHeadDim + 16 * i);
       rope_chunk_pair<T>(u0, u1, tab, p.is_neox != 0);

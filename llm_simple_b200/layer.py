@@ -12,7 +12,7 @@ EXPORTS = [
     "gpu_allocator_set_limit", "gpu_allocator_use_host_backend", "gpu_init_freq_cis",
     "gpu_attention_layer_create", "gpu_attention_layer_destroy", "gpu_attention_layer_forward",
     "gpu_attention_layer_decode_ragged", "gpu_attention_layer_set_shared_lens",
-    "gpu_attention_layer_forward_host", "gpu_attention_layer_cache",
+    "gpu_attention_layer_forward_host", "gpu_attention_layer_forward_fused", "gpu_attention_layer_cache",
 ]
 
 LLAMA2, QWEN2 = 0, 1
@@ -39,6 +39,7 @@ def lib():
         L.gpu_attention_layer_decode_ragged.argtypes = [vp] * 6 + [i, vp]
         L.gpu_attention_layer_set_shared_lens.argtypes = [vp, vp, i, ctypes.c_long]
         L.gpu_attention_layer_forward_host.argtypes = [vp, vp, vp, i, i, i, vp, vp]
+        L.gpu_attention_layer_forward_fused.argtypes = [vp, vp, vp, vp, i, i, i, vp, vp]
         L.gpu_attention_layer_cache.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
         _ready = True
     return L
@@ -102,6 +103,15 @@ class AttentionLayer:
             lens_ptr = lens.ctypes.data
         ops._check(lib().gpu_attention_layer_forward_host(self.h, ops._ptr(out_host), ops._ptr(qkv_host), batch,
                                                           cur_pos, prev_pos, lens_ptr, ops._stream(stream)))
+
+    def forward_fused(self, out, qkv, bias, batch, cur_pos, prev_pos, kv_len=None, stream=None):
+        """Device tensors: qkv [batch][cur_size][(H + 2 kvH)*D], bias one such row or None."""
+        lens_ptr = None
+        if kv_len is not None:
+            lens = np.ascontiguousarray(kv_len, dtype=np.int32)
+            lens_ptr = lens.ctypes.data
+        ops._check(lib().gpu_attention_layer_forward_fused(self.h, ops._ptr(out), ops._ptr(qkv), ops._ptr(bias), batch,
+                                                           cur_pos, prev_pos, lens_ptr, ops._stream(stream)))
 
     def cache_ptrs(self):
         k, v = ctypes.c_void_p(), ctypes.c_void_p()

@@ -19,7 +19,8 @@ _lib = None
 
 EXPORTS = [
     "gpu_flash_attn_layer", "gpu_flash_attn_gqa_layer", "gpu_flash_attn_opt_prefill_layer",
-    "gpu_rope_layer", "gpu_rope_single_layer", "gpu_rope_kv_append_layer", "gpu_attn_prefill_layer",
+    "gpu_rope_layer", "gpu_rope_single_layer", "gpu_split_qkv_layer", "gpu_rope_kv_append_layer",
+    "gpu_qkv_rope_kv_append_layer", "gpu_bias_add_layer", "gpu_attn_prefill_layer",
     "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
@@ -83,6 +84,9 @@ def lib():
         L.gpu_rope_layer.argtypes = [vp] * 5 + [i] * 6 + [vp]
         L.gpu_rope_single_layer.argtypes = [vp] * 3 + [i] * 6 + [vp]
         L.gpu_rope_kv_append_layer.argtypes = [dp] + [vp] * 7 + [i32p, i, i, vp]
+        L.gpu_qkv_rope_kv_append_layer.argtypes = [dp] + [vp] * 4 + [ctypes.c_int64] * 2 + [vp, vp, i32p, i, i, vp]
+        L.gpu_split_qkv_layer.argtypes = [vp] * 4 + [i] * 5 + [vp]
+        L.gpu_bias_add_layer.argtypes = [vp] * 3 + [i, i, ctypes.c_int64, i, vp]
         L.gpu_attn_prefill_layer.argtypes = [dp] + [vp] * 4 + [i, i, vp]
         L.gpu_attn_decode_layer.argtypes = [dp, vp, f32p, f32p] + [vp] * 6 + [i32p, i32p, i, i, vp,
                                                                                ctypes.c_size_t, vp]
@@ -159,6 +163,23 @@ def gpu_rope_kv_append_layer(desc, q_out, k_cache, v_cache, q_in, k_in, v_in, fr
     _check(lib().gpu_rope_kv_append_layer(ctypes.byref(desc), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
                                           _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(freqs_cis),
                                           _ptr(start_pos_dev), start_pos, m, _stream(stream)))
+
+
+def gpu_qkv_rope_kv_append_layer(desc, q_out, k_cache, v_cache, qkv_in, qkv_seq_stride, qkv_tok_stride, qkv_bias,
+                                 freqs_cis, start_pos_dev, start_pos, m, stream=None):
+    """RoPE + append fed from a fused [q | k | v] projection row, optional bias row."""
+    _check(lib().gpu_qkv_rope_kv_append_layer(ctypes.byref(desc), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                              _ptr(qkv_in), qkv_seq_stride, qkv_tok_stride, _ptr(qkv_bias),
+                                              _ptr(freqs_cis), _ptr(start_pos_dev), start_pos, m, _stream(stream)))
+
+
+def gpu_bias_add_layer(out, x, bias, rows, width, row_stride, dt, stream=None):
+    _check(lib().gpu_bias_add_layer(_ptr(out), _ptr(x), _ptr(bias), rows, width, row_stride, dt, _stream(stream)))
+
+
+def gpu_split_qkv_layer(out_q, out_k, out_v, qkv, batch, q_dim, k_dim, v_dim, dt, stream=None):
+    _check(lib().gpu_split_qkv_layer(_ptr(out_q), _ptr(out_k), _ptr(out_v), _ptr(qkv), batch, q_dim, k_dim, v_dim,
+                                     dt, _stream(stream)))
 
 
 def gpu_attn_prefill_layer(desc, out, q, k_cache, v_cache, m, offset, stream=None):

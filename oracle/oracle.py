@@ -120,6 +120,24 @@ def rope_layer(q, k, freqs_cis, start_pos, n_heads, is_neox, dt):
     return oq, ok
 
 
+def split_qkv(qkv, q_dim, k_dim, v_dim):
+    """Row-wise split of a fused projection output [rows][q_dim + k_dim + v_dim] into
+    three dense arrays: the definition of npu_split_qkv_layer (prebuild/npu_ops.h:27-30;
+    the reference ships no CPU twin and no test of it)."""
+    qkv = np.ascontiguousarray(qkv)
+    assert qkv.shape[-1] == q_dim + k_dim + v_dim
+    return (np.ascontiguousarray(qkv[..., :q_dim]), np.ascontiguousarray(qkv[..., q_dim:q_dim + k_dim]),
+            np.ascontiguousarray(qkv[..., q_dim + k_dim:]))
+
+
+def bias_add(x, bias, dt):
+    """round_dt(float(x) + float(bias)), bias broadcast over rows: a projection whose
+    epilogue adds the bias (npu_matmul_bias_nz_layer, prebuild/npu_ops.h:90-92, as the
+    Qwen2 q/k/v projections use it, src/llama2_layer_npu.cpp:1174-1177) rounds once, here
+    the projection output is already 16-bit, so this is the second rounding point."""
+    return to_bits(to_f32(x, dt) + to_f32(bias, dt), dt)
+
+
 def kv_append(k_cache, v_cache, k_emb, v, prev_pos, kv_heads, head_dim):
     """In place, token-major caches [max_pos][kv_heads][head_dim]."""
     cur_size = k_emb.shape[0]

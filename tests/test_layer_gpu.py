@@ -114,6 +114,45 @@ def test_host_buffer_prefill_matches_device_prefill(layer):
     b.close()
 
 
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_fused_projection_row_prefill_then_decode(layer, with_bias):
+    """forward_fused on a packed q|k|v row (+ bias row) equals forward on the split, biased tensors bit for bit:
+    prefill of a prompt, then ragged one-token steps of a batch of 3."""
+    H, kvh, dt, neox, theta, max_seq, batch = 12, 2, BF16, True, 1e6, 256, 3
+    width = (H + 2 * kvh) * D
+    bias = rnd_bits((width,), dt, 40) if with_bias else None
+    a = layer.AttentionLayer(layer.QWEN2, H, kvh, max_seq, batch, dt, theta, neox)
+    b = layer.AttentionLayer(layer.QWEN2, H, kvh, max_seq, batch, dt, theta, neox)
+    bias_d = dev(bias, dt) if with_bias else None
+
+    def split_biased(rows):
+        x = orc.bias_add(rows, bias, dt) if with_bias else rows
+        return orc.split_qkv(x, H * D, kvh * D, kvh * D)
+
+    m = 130
+    rows = rnd_bits((batch, m, width), dt, 41)
+    q, k, v = split_biased(rows)
+    out_a = torch.empty((batch, m, H * D), dtype=torch.bfloat16, device="cuda")
+    out_b = torch.empty_like(out_a)
+    a.forward(out_a, dev(q, dt), dev(k, dt), dev(v, dt), batch, m, 0)
+    b.forward_fused(out_b, dev(rows, dt), bias_d, batch, m, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16))
+    lens = np.array([m, m, m], dtype=np.int32)
+    for step in range(3):
+        rows = rnd_bits((batch, 1, width), dt, 50 + step)
+        q, k, v = split_biased(rows)
+        o_a = torch.empty((batch, H * D), dtype=torch.bfloat16, device="cuda")
+        o_b = torch.empty_like(o_a)
+        a.decode_ragged(o_a, dev(q, dt), dev(k, dt), dev(v, dt), lens)
+        b.forward_fused(o_b, dev(rows, dt), bias_d, batch, int(lens[0]) + 1, int(lens[0]), kv_len=lens)
+        torch.cuda.synchronize()
+        assert torch.equal(o_a.view(torch.int16), o_b.view(torch.int16)), "decode step %d" % step
+        lens = lens + 1
+    a.close()
+    b.close()
+
+
 def test_pooled_temporaries_are_recycled(layer):
     """A freed device block goes back to GPUAllocator's pool and serves the next request of that size."""
     L = layer.lib()
