@@ -208,6 +208,10 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling on a small case)")
     ap.add_argument("--batch", type=int, default=None, help="override the batch (profiling on a small case)")
     ap.add_argument("--no-extras", action="store_true", help="skip prefill leg, e2e and CPU baseline")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="on ONE GPU, run rank 0's shard of an N-way KV-head split (sizing a multi-GPU shard)")
+    ap.add_argument("--graph", type=int, default=1,
+                    help="1: replay the step's launches from a CUDA graph (default), 0: launch them one by one")
     ap.add_argument("--leg", default="all", choices=["all", "prefill"],
                     help="prefill: run only the prefill leg (small, for profiling) and print its object")
     args = ap.parse_args()
@@ -258,7 +262,10 @@ def main():
     H, kvh = cfg["n_heads"], cfg["n_kv_heads"]
     if kvh % world:
         raise SystemExit("KV heads (%d) do not divide over %d ranks" % (kvh, world))
-    kvh_l, H_l = kvh // world, H // world
+    split = world * max(args.shard_of, 1)
+    if kvh % split:
+        raise SystemExit("KV heads (%d) do not divide into %d shards" % (kvh, split))
+    kvh_l, H_l = kvh // split, H // split
     layers, batch = cfg["layers"], cfg["batch"]
     max_pos = cfg["len_hi"] + 8
     max_kv = max(lens) + 1
@@ -293,6 +300,31 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    launch_step = step
+    graph = None
+    if args.graph:
+        # A decode step is a fixed sequence of launches: capture it once and replay it, as a
+        # serving loop would; this removes the per-call host cost (a few per cent of the step).
+        step()
+        barrier()
+        ops.gpu_ops_launch_count(True)
+        try:
+            cap = torch.cuda.Stream(device=dev)
+            graph = torch.cuda.CUDAGraph()
+            stream = cap
+            with torch.cuda.stream(cap):
+                graph.capture_begin()
+                launch_step()
+                graph.capture_end()
+        except Exception as e:  # capture unavailable: launch call by call
+            sys.stderr.write("cuda graph capture failed (%s); launching call by call\n" % e)
+            graph = None
+        launches_per_step = ops.gpu_ops_launch_count(True)
+        stream = torch.cuda.current_stream()
+        if graph is not None:
+            def step():
+                graph.replay()
+
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
@@ -306,6 +338,8 @@ def main():
         ev1.record(stream)
         barrier()
     launches = ops.gpu_ops_launch_count(True)
+    if graph is not None:
+        launches = launches_per_step * args.steps   # kernels replayed from the graph
     ms = ev0.elapsed_time(ev1)
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -315,7 +349,8 @@ def main():
         dist.all_reduce(lt)
         launches = int(lt.item())
     ms_per_step = ms / args.steps
-    bytes_layer_all = decode_bytes([L + 1 for L in lens], H, kvh)         # all ranks, one layer
+    so = max(args.shard_of, 1)
+    bytes_layer_all = decode_bytes([L + 1 for L in lens], H // so, kvh // so)  # all ranks, one layer
     bytes_layer_rank = decode_bytes([L + 1 for L in lens], H_l, kvh_l)    # this rank, one layer
     value = bytes_layer_all * layers / (ms_per_step * 1e-3) / 1e9
     layer_ms = ms_per_step / layers
@@ -338,7 +373,11 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg["name"], "layers": layers, "batch": batch, "n_heads": H, "n_kv_heads": kvh,
                    "head_dim": D, "kv_len": "uniform[%d,%d] seed %d" % (cfg["len_lo"], cfg["len_hi"], cfg["seed"]),
-                   "sharding": "kv-head x%d" % world, "cache_layout": "head-major",
+                   "sharding": "kv-head x%d" % world if args.shard_of <= 1 else
+                               "rank 0's shard of a kv-head x%d split, alone on one GPU" % split,
+                   "launch": "cuda graph of the step's %d launches" % launches_per_step if graph is not None
+                             else "one call per layer",
+                   "cache_layout": "head-major",
                    "l2": "inputs larger than L2 (%.0f MB per layer, %.1f GB per step per rank)"
                          % (bytes_layer_rank / 1e6, bytes_layer_rank * layers / 1e9)},
         "roofline": roofline, "clocks": clk.summary(), "gpu_launches": launches,

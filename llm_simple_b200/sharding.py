@@ -12,6 +12,9 @@ counterpart there):
   normalised partial output with its log-sum-exp; the partials are all-gathered
   into local memory and merged locally (gpu_attn_merge_packed_layer).  The owner
   of the tail slice appends the new token.
+
+Moving from the first partition (how a prompt is prefilled) to the second (how a
+very long context is decoded) is one exchange: reshard_heads_to_positions().
 """
 
 
@@ -39,6 +42,73 @@ def packed_partial_floats(rows, head_dim=128):
     """Floats one rank contributes to the (O, LSE) exchange: rows*head_dim outputs
     followed by rows log-sum-exps."""
     return rows * (head_dim + 1)
+
+
+def reshard_plan(kv_lens, n_kv_heads, world, rank):
+    """Chunks that move when a cache sharded by KV head becomes a cache sharded by position.
+
+    Returns (sends, recvs).  A send is (peer, seq, local_head, lo, hi): positions [lo, hi) of
+    one of this rank's heads, which `peer` owns after the exchange.  A recv is (peer, seq,
+    head, n): n positions of global KV head `head` arriving from its old owner, stored at
+    local positions [0, n).  Both lists are ordered by (peer, seq, head), the order in which
+    the two sides post their transfers, so that they pair up."""
+    h_lo, h_hi = kv_head_range(n_kv_heads, world, rank)
+    per = h_hi - h_lo
+    sends, recvs = [], []
+    for peer in range(world):
+        for b, total in enumerate(kv_lens):
+            sl = position_slices(int(total), world)
+            lo, hi = sl[peer]
+            if hi > lo:
+                for h in range(per):
+                    sends.append((peer, b, h, lo, hi))
+            mine = sl[rank][1] - sl[rank][0]
+            if mine > 0:
+                for h in range(per):
+                    recvs.append((peer, b, peer * per + h, mine))
+    return sends, recvs
+
+
+def reshard_heads_to_positions(k_src, v_src, k_dst, v_dst, kv_lens, group=None):
+    """Head-sharded caches -> position-sharded caches, in place in the destination tensors.
+
+    k_src / v_src  [batch][kvH/P][max_pos][D]: this rank's KV heads, all positions (the layout a
+                   head-sharded prefill leaves behind)
+    k_dst / v_dst  [batch][kvH][cap][D]: all KV heads, this rank's position slice
+                   (position_slices(kv_lens[b], P)[rank]) stored from local position 0
+    kv_lens        cached positions per sequence, the same list on every rank
+    Every chunk (one head, one sequence, one destination) is contiguous on both sides, so the
+    exchange is a group of point-to-point transfers straight between the caches, with no staging
+    copy; the chunk a rank keeps is a local copy.  Works on CUDA tensors (NCCL) and on CPU
+    tensors (gloo)."""
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    n_kv_heads = k_dst.shape[1]
+    if k_src.shape[1] * world != n_kv_heads:
+        raise ValueError("source holds %d heads per rank, destination %d heads, %d ranks"
+                         % (k_src.shape[1], n_kv_heads, world))
+    sends, recvs = reshard_plan(kv_lens, n_kv_heads, world, rank)
+    ops_list = []
+    local = [(b, h, lo, hi) for (peer, b, h, lo, hi) in sends if peer == rank]
+    for src, dst in ((k_src, k_dst), (v_src, v_dst)):
+        for peer, b, h, lo, hi in sends:
+            if peer != rank:
+                ops_list.append(dist.P2POp(dist.isend, src[b, h, lo:hi], _global_rank(dist, group, peer), group))
+        for peer, b, gh, n in recvs:
+            if peer != rank:
+                if n > dst.shape[2]:
+                    raise ValueError("slice of %d positions does not fit a destination of %d" % (n, dst.shape[2]))
+                ops_list.append(dist.P2POp(dist.irecv, dst[b, gh, :n], _global_rank(dist, group, peer), group))
+        per = k_src.shape[1]
+        for b, h, lo, hi in local:
+            dst[b, rank * per + h, :hi - lo].copy_(src[b, h, lo:hi])
+    if ops_list:
+        for req in dist.batch_isend_irecv(ops_list):
+            req.wait()
+
+
+def _global_rank(dist, group, group_rank):
+    return group_rank if group is None else dist.get_global_rank(group, group_rank)
 
 
 class SplitKVDecoder:

@@ -115,3 +115,93 @@ def test_two_ranks_head_sharding_and_split_kv_exchange():
     gold = orc.attn(q_r, kc_t, vc_t, 1, L + 1, L, H // kvh, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
     assert_parity(split0, gold, dt, "rank 0")
     assert np.array_equal(split0, split1)
+
+
+def _flow_case():
+    dt, H, kvh, neox, theta, prompt = BF16, 40, 8, True, 1e6, 700
+    max_pos = 768
+    table = orc.init_freq_cis(D, max_pos, theta, dt)
+    q = rnd_bits((prompt + 1, H * D), dt, 11)           # prompt rows, then the first generated token
+    k, v = rnd_bits((prompt + 1, kvh * D), dt, 12), rnd_bits((prompt + 1, kvh * D), dt, 13)
+    return dt, H, kvh, neox, prompt, max_pos, table, q, k, v
+
+
+def _flow_rank(rank, world, port, ret):
+    """Prompt prefilled with the cache sharded by KV head, cache re-sharded by position over
+    NCCL, first token decoded over the position shards with the (O, LSE) exchange."""
+    import torch.distributed as dist
+    from llm_simple_b200 import ops, sharding
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dt, H, kvh, neox, prompt, max_pos, table, q, k, v = _flow_case()
+        g = H // kvh
+        lo, hi = sharding.kv_head_range(kvh, world, rank)
+        kvh_l, H_l = hi - lo, (hi - lo) * g
+        tab_d = torch.from_numpy(table).cuda()
+        qs = np.ascontiguousarray(q[:prompt].reshape(prompt, H, D)[:, lo * g:hi * g].reshape(prompt, -1))
+        ks = np.ascontiguousarray(k[:prompt].reshape(prompt, kvh, D)[:, lo:hi].reshape(prompt, -1))
+        vs = np.ascontiguousarray(v[:prompt].reshape(prompt, kvh, D)[:, lo:hi].reshape(prompt, -1))
+        desc_p = ops.make_desc(dt, 1, H_l, kvh_l, prompt, max_pos, layout="head", is_neox=neox)
+        k_src = torch.zeros((1, kvh_l, max_pos, D), dtype=torch.bfloat16, device="cuda")
+        v_src = torch.zeros_like(k_src)
+        q_emb = torch.empty((prompt, H_l * D), dtype=torch.bfloat16, device="cuda")
+        out_p = torch.empty_like(q_emb)
+        ops.gpu_rope_kv_append_layer(desc_p, q_emb, k_src, v_src, dev(qs, dt), dev(ks, dt), dev(vs, dt), tab_d, None,
+                                     0, prompt)
+        ops.gpu_attn_prefill_layer(desc_p, out_p, q_emb, k_src, v_src, prompt, 0)
+        # ---- head shards -> position shards
+        sl_lo, sl_hi = sharding.position_slices(prompt, world)[rank]
+        cap = sl_hi - sl_lo + 8
+        k_dst = torch.zeros((1, kvh, cap, D), dtype=torch.bfloat16, device="cuda")
+        v_dst = torch.zeros_like(k_dst)
+        torch.cuda.synchronize()
+        sharding.reshard_heads_to_positions(k_src, v_src, k_dst, v_dst, [prompt])
+        torch.cuda.synchronize()
+        # ---- first generated token over the position shards
+        desc_d = ops.make_desc(dt, 1, H, kvh, 1, cap, layout="head", is_neox=neox)
+        dec = sharding.SplitKVDecoder(desc_d, dt)
+        ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc_d, cap)
+        ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+        out = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
+        dec.step(out, dev(q[prompt:], dt), dev(k[prompt:], dt), dev(v[prompt:], dt), k_dst, v_dst, tab_d,
+                 torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
+                 torch.tensor([prompt], dtype=torch.int32, device="cuda"), sl_hi - sl_lo, ws, ws_bytes)
+        torch.cuda.synchronize()
+        ret[rank] = (host(k_dst[0, :, :sl_hi - sl_lo]), host(v_dst[0, :, :sl_hi - sl_lo]), host(out), host(out_p))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_prefill_reshard_decode_flow():
+    import torch.multiprocessing as mp
+    from llm_simple_b200 import sharding
+    world, port = 2, _free_port()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_flow_rank, args=(world, port, ret), nprocs=world, join=True)
+    dt, H, kvh, neox, prompt, max_pos, table, q, k, v = _flow_case()
+    g = H // kvh
+    k_rot = orc.rope_single_layer(k[:prompt], table, 0, kvh, neox, dt).reshape(prompt, kvh, D)
+    q_rot = orc.rope_single_layer(q[:prompt], table, 0, H, neox, dt)
+    gold_p = orc.attn(q_rot, k_rot.reshape(prompt, -1), v[:prompt], prompt, prompt, 0, g, kvh, D, dt, orc.MODE_GOLDEN,
+                      threads=8).reshape(prompt, H, D)
+    for r in range(world):
+        lo, hi = sharding.position_slices(prompt, world)[r]
+        k_got, v_got, _, out_p = ret[r]
+        # the re-sharded slices hold exactly the rotated K and the raw V of their positions, all heads
+        assert np.array_equal(k_got, k_rot[lo:hi].transpose(1, 0, 2))
+        assert np.array_equal(v_got, v[lo:hi].reshape(hi - lo, kvh, D).transpose(1, 0, 2))
+        h_lo, h_hi = sharding.kv_head_range(kvh, world, r)
+        assert_parity(out_p, gold_p[:, h_lo * g:h_hi * g].reshape(prompt, -1), dt, "prefill rank %d" % r)
+    # the decoded token equals attention over the whole prompt + itself
+    kc_t = np.zeros((prompt + 1, kvh * D), np.uint16)
+    vc_t = np.zeros((prompt + 1, kvh * D), np.uint16)
+    kc_t[:prompt], vc_t[:prompt] = k_rot.reshape(prompt, -1), v[:prompt]
+    q_r = orc.rope_single_layer(q[prompt:], table, prompt, H, neox, dt)
+    k_r = orc.rope_single_layer(k[prompt:], table, prompt, kvh, neox, dt)
+    orc.kv_append(kc_t, vc_t, k_r, v[prompt:], prompt, kvh, D)
+    gold = orc.attn(q_r, kc_t, vc_t, 1, prompt + 1, prompt, g, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
+    assert_parity(ret[0][2], gold, dt, "decode after re-shard, rank 0")
+    assert np.array_equal(ret[0][2], ret[1][2])

@@ -86,3 +86,52 @@ def test_partial_exchange_over_gloo_two_ranks_equals_full_attention():
     ret = mp.get_context("spawn").Manager().dict()
     mp.spawn(_rank_main, args=(world, port, ret), nprocs=world, join=True)
     assert len(ret) == world and all(err < 2e-6 for err in ret.values()), dict(ret)
+
+
+def test_reshard_plan_pairs_up():
+    """Every chunk one rank sends is a chunk its peer expects, in the same order."""
+    lens, kvh, world = [10, 3, 0, 17], 4, 4
+    plans = [sharding.reshard_plan(lens, kvh, world, r) for r in range(world)]
+    per = kvh // world
+    for a in range(world):
+        for b in range(world):
+            sent = [(seq, a * per + h, hi - lo) for (peer, seq, h, lo, hi) in plans[a][0] if peer == b]
+            got = [(seq, gh, n) for (peer, seq, gh, n) in plans[b][1] if peer == a]
+            assert sent == got
+    # all positions of all heads are covered exactly once
+    total = sum(hi - lo for pl in plans for (_, _, _, lo, hi) in pl[0])
+    assert total == sum(lens) * kvh
+
+
+def _reshard_rank(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        batch, kvh, max_pos, lens = 3, 4, 40, [37, 5, 1]
+        rng = np.random.default_rng(9)                      # the same full cache on every rank
+        full_k = rng.integers(0, 65536, size=(batch, kvh, max_pos, D)).astype(np.int16)
+        full_v = rng.integers(0, 65536, size=(batch, kvh, max_pos, D)).astype(np.int16)
+        lo_h, hi_h = sharding.kv_head_range(kvh, world, rank)
+        k_src = torch.from_numpy(full_k[:, lo_h:hi_h].copy())
+        v_src = torch.from_numpy(full_v[:, lo_h:hi_h].copy())
+        cap = 20
+        k_dst = torch.full((batch, kvh, cap, D), -1, dtype=torch.int16)
+        v_dst = torch.full((batch, kvh, cap, D), -1, dtype=torch.int16)
+        sharding.reshard_heads_to_positions(k_src, v_src, k_dst, v_dst, lens)
+        ok = True
+        for b, total in enumerate(lens):
+            lo, hi = sharding.position_slices(total, world)[rank]
+            n = hi - lo
+            ok &= np.array_equal(k_dst[b, :, :n].numpy(), full_k[b, :, lo:hi])
+            ok &= np.array_equal(v_dst[b, :, :n].numpy(), full_v[b, :, lo:hi])
+            ok &= bool((k_dst[b, :, n:] == -1).all()) and bool((v_dst[b, :, n:] == -1).all())
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reshard_heads_to_positions_two_ranks_gloo():
+    world, port = 2, _free_port()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_reshard_rank, args=(world, port, ret), nprocs=world, join=True)
+    assert dict(ret) == {0: True, 1: True}
