@@ -227,6 +227,42 @@ int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const vo
 /* Scratch bytes gpu_attn_decode_layer needs for this geometry and bound. */
 size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len);
 
+/* ------------------------------------------------------------------------
+ * Paged KV cache.  The reference allocates one flat block per layer
+ * (src/llama2_layer_npu.cpp:1148-1149); for batched serving the cache is a
+ * pool of fixed-size pages and a per-sequence page table instead.
+ * ------------------------------------------------------------------------ */
+
+/* Position pos of sequence b lives in page page_table[b*table_stride + pos/page_size]
+ * of the pool, at in-page position pos % page_size.  Inside a page the
+ * descriptor's cache_head_stride / cache_pos_stride apply (head-major page
+ * [kv_head][page_size][D]: head stride page_size*D, position stride D);
+ * cache_seq_stride is not used.  page_size: a power of two >= 64.  All strides
+ * in elements.  Pages named by the table for positions the call touches must
+ * exist; the table is read by the kernels, never written. */
+typedef struct gpu_kv_pages {
+  const int32_t *page_table; /* device, int32 [batch][table_stride] */
+  int32_t table_stride;
+  int32_t page_size;
+  int64_t page_stride;       /* elements between consecutive pages of the pool */
+} gpu_kv_pages;
+
+/* gpu_rope_kv_append_layer writing K and V through the page table. */
+int gpu_rope_kv_append_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages,
+                                   void *q_out, void *k_pool, void *v_pool, const void *q_in,
+                                   const void *k_in, const void *v_in, const void *freqs_cis_dev,
+                                   const int32_t *start_pos_dev, int start_pos, int m,
+                                   gpu_stream_t stream);
+
+/* gpu_attn_decode_layer over a paged cache (final output only; same workspace
+ * sizing, same split and merge kernels; the page of position kv_len[b] must be
+ * in the table when append_new is set). */
+int gpu_attn_decode_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out,
+                                const void *q_in, const void *k_in, const void *v_in,
+                                void *k_pool, void *v_pool, const void *freqs_cis_dev,
+                                const int32_t *kv_len_dev, int append_new, int max_kv_len,
+                                void *workspace, size_t workspace_bytes, gpu_stream_t stream);
+
 /* Merge n_parts partial results: o_parts fp32 [n_parts][rows][head_dim]
  * (normalised), lse_parts fp32 [n_parts][rows] (natural log).
  * out[row] = sum_p exp(lse_p - M) o_p / sum_p exp(lse_p - M), M = max_p lse_p,

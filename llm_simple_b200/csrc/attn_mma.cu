@@ -62,21 +62,33 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
   const int rows = p.m * G;
   const bool has_new = p.append && pos_end == total;
 
-  const T *kbase = static_cast<const T *>(p.k_cache) + b * p.g.c_seq + kvh * p.g.c_head;
-  const T *vbase = static_cast<const T *>(p.v_cache) + b * p.g.c_seq + kvh * p.g.c_head;
+  // flat cache: the sequence's block; paged cache: the pool, pages looked up per tile
+  const bool paged = p.pg.table != nullptr;
+  const int32_t *ptab = paged ? p.pg.table + static_cast<long>(b) * p.pg.table_stride : nullptr;
+  const long seq_off = paged ? 0 : b * p.g.c_seq;
+  const T *kbase = static_cast<const T *>(p.k_cache) + seq_off + kvh * p.g.c_head;
+  const T *vbase = static_cast<const T *>(p.v_cache) + seq_off + kvh * p.g.c_head;
+  // element offset of cache position pos (which must exist) from kbase / vbase
+  auto pos_off = [&](int pos) -> long {
+    if (!paged) return static_cast<long>(pos) * p.g.c_pos;
+    return static_cast<long>(ptab[pos >> p.pg.page_shift]) * p.pg.page_stride +
+           static_cast<long>(pos & ((1 << p.pg.page_shift) - 1)) * p.g.c_pos;
+  };
 
   const int ntiles = (pos_end - pos0 + kTileN - 1) / kTileN;
   auto load_tile = [&](int t) {
     const int tpos = pos0 + t * kTileN;
     const uint32_t ks = smem_u32(stage_s + (t % kDecodeStages) * 2 * kTileBytes);
     const uint32_t vs = ks + kTileBytes;
+    // a tile of 64 positions starts at a multiple of 64 and so lies inside one page
+    const long tile_off = tpos < load_end ? pos_off(tpos) : 0;
 #pragma unroll
     for (int it = 0; it < kTileN * 16 / kDecodeThreads; ++it) {
       const int cidx = tid + it * kDecodeThreads;
       const int row = cidx >> 4, chunk = cidx & 15;
       const int pos = tpos + row;
       const bool valid = pos < load_end;
-      const long off = valid ? pos * p.g.c_pos + chunk * 8 : 0;
+      const long off = valid ? tile_off + row * p.g.c_pos + chunk * 8 : 0;
       cp_async16(ks + swz_off(row, chunk), kbase + off, valid ? 16 : 0);
       cp_async16(vs + swz_off(row, chunk), vbase + off, valid ? 16 : 0);
     }
@@ -127,8 +139,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
     T *sdst = is_k ? knew_s : vnew_s;
     *reinterpret_cast<uint4 *>(sdst + c0 * 8) = u0;
     *reinterpret_cast<uint4 *>(sdst + c1 * 8) = u1;
-    T *gdst = static_cast<T *>(is_k ? p.k_cache : p.v_cache) + b * p.g.c_seq + kvh * p.g.c_head +
-              static_cast<long>(len_old) * p.g.c_pos;
+    T *gdst = static_cast<T *>(is_k ? p.k_cache : p.v_cache) + seq_off + kvh * p.g.c_head + pos_off(len_old);
     *reinterpret_cast<uint4 *>(gdst + c0 * 8) = u0;
     *reinterpret_cast<uint4 *>(gdst + c1 * 8) = u1;
   }

@@ -259,6 +259,25 @@ void set_last_error(const char *msg) { g_last_error = msg ? msg : ""; }
 
 namespace {
 
+// Validates a page description and converts it; pages == nullptr means a flat cache.
+int paging_from(const gpu_kv_pages *pages, KvPaging *pg) {
+  *pg = KvPaging{};
+  if (!pages) return GPU_OPS_OK;
+  if (!pages->page_table) return fail(GPU_OPS_E_INVALID, "null page table");
+  const int ps = pages->page_size;
+  if (ps < 64 || (ps & (ps - 1))) return fail(GPU_OPS_E_UNSUPPORTED, "page size %d: a power of two >= 64", ps);
+  if (pages->table_stride <= 0 || pages->page_stride <= 0 || pages->page_stride % 8)
+    return fail(GPU_OPS_E_INVALID, "table stride %d, page stride %lld", pages->table_stride,
+                static_cast<long long>(pages->page_stride));
+  pg->table = pages->page_table;
+  pg->page_stride = pages->page_stride;
+  pg->table_stride = pages->table_stride;
+  int shift = 0;
+  while ((1 << shift) < ps) ++shift;
+  pg->page_shift = shift;
+  return GPU_OPS_OK;
+}
+
 // Sources of one RoPE + append pass: three tensors with their own strides, or three
 // column ranges of one fused projection row; bias rows are optional.
 struct RopeSources {
@@ -267,10 +286,12 @@ struct RopeSources {
   const void *bias_q, *bias_k, *bias_v;
 };
 
-int rope_append_common(const gpu_attn_desc *desc, void *q_out, void *k_cache, void *v_cache, const RopeSources &src,
-                       const void *freqs_cis_dev, const int32_t *start_pos_dev, int start_pos, int m,
-                       gpu_stream_t stream) {
+int rope_append_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *q_out, void *k_cache, void *v_cache,
+                       const RopeSources &src, const void *freqs_cis_dev, const int32_t *start_pos_dev, int start_pos,
+                       int m, gpu_stream_t stream) {
   const void *q_in = src.q, *k_in = src.k, *v_in = src.v;
+  KvPaging pg;
+  if (int rc = paging_from(pages, &pg)) return rc;
   if (!k_cache || !v_cache || !k_in || !v_in || !freqs_cis_dev || (q_out && !q_in))
     return fail(GPU_OPS_E_INVALID, "null tensor pointer");
   if (m < 0 || (!start_pos_dev && start_pos < 0)) return fail(GPU_OPS_E_INVALID, "m %d, start_pos %d", m, start_pos);
@@ -310,6 +331,7 @@ int rope_append_common(const gpu_attn_desc *desc, void *q_out, void *k_cache, vo
     s.dst_head = desc->cache_head_stride;
   }
   p.slots = (q_out ? desc->n_heads : 0) + 2 * desc->n_kv_heads;
+  p.pg = pg;
   p.freqs_cis = static_cast<const float *>(freqs_cis_dev);
   p.start_pos_dev = start_pos_dev;
   p.start_pos = start_pos;
@@ -364,7 +386,20 @@ int gpu_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cac
   if (int rc = check_desc(desc)) return rc;
   RopeSources src{q_in, k_in, v_in, desc->q_seq_stride, desc->q_tok_stride, desc->kv_in_seq_stride,
                   desc->kv_in_tok_stride, nullptr, nullptr, nullptr};
-  return rope_append_common(desc, q_out, k_cache, v_cache, src, freqs_cis_dev, start_pos_dev, start_pos, m, stream);
+  return rope_append_common(desc, nullptr, q_out, k_cache, v_cache, src, freqs_cis_dev, start_pos_dev, start_pos, m,
+                            stream);
+}
+
+int gpu_rope_kv_append_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *q_out, void *k_pool,
+                                   void *v_pool, const void *q_in, const void *k_in, const void *v_in,
+                                   const void *freqs_cis_dev, const int32_t *start_pos_dev, int start_pos, int m,
+                                   gpu_stream_t stream) {
+  if (int rc = check_desc(desc)) return rc;
+  if (!pages) return fail(GPU_OPS_E_INVALID, "null page description");
+  RopeSources src{q_in, k_in, v_in, desc->q_seq_stride, desc->q_tok_stride, desc->kv_in_seq_stride,
+                  desc->kv_in_tok_stride, nullptr, nullptr, nullptr};
+  return rope_append_common(desc, pages, q_out, k_pool, v_pool, src, freqs_cis_dev, start_pos_dev, start_pos, m,
+                            stream);
 }
 
 int gpu_qkv_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k_cache, void *v_cache,
@@ -392,7 +427,8 @@ int gpu_qkv_rope_kv_append_layer(const gpu_attn_desc *desc, void *q_out, void *k
                   bias,
                   bias ? bias + q_dim * eb : nullptr,
                   bias ? bias + (q_dim + kv_dim) * eb : nullptr};
-  return rope_append_common(desc, q_out, k_cache, v_cache, src, freqs_cis_dev, start_pos_dev, start_pos, m, stream);
+  return rope_append_common(desc, nullptr, q_out, k_cache, v_cache, src, freqs_cis_dev, start_pos_dev, start_pos, m,
+                            stream);
 }
 
 int gpu_split_qkv_layer(void *output_q_dev, void *output_k_dev, void *output_v_dev, const void *input_qkv, int batch,
@@ -488,12 +524,14 @@ size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len
   return decode_ws_bytes(static_cast<long>(desc->batch) * desc->n_heads, splits);
 }
 
-int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial, float *lse_partial,
-                          const void *q_in, const void *k_in, const void *v_in, void *k_cache, void *v_cache,
-                          const void *freqs_cis_dev, const int32_t *kv_len_dev, const int32_t *rope_pos_dev,
-                          int append_new, int max_kv_len, void *workspace, size_t workspace_bytes,
-                          gpu_stream_t stream) {
+static int decode_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out, float *o_partial,
+                         float *lse_partial, const void *q_in, const void *k_in, const void *v_in, void *k_cache,
+                         void *v_cache, const void *freqs_cis_dev, const int32_t *kv_len_dev,
+                         const int32_t *rope_pos_dev, int append_new, int max_kv_len, void *workspace,
+                         size_t workspace_bytes, gpu_stream_t stream) {
   if (int rc = check_desc(desc)) return rc;
+  KvPaging pg;
+  if (int rc = paging_from(pages, &pg)) return rc;
   const int group = desc->n_heads / desc->n_kv_heads;
   if (group > 16) return fail(GPU_OPS_E_UNSUPPORTED, "group size %d: at most 16 query heads per KV head", group);
   if (!q_in || !k_cache || !v_cache || !freqs_cis_dev || !kv_len_dev)
@@ -526,6 +564,7 @@ int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial
   p.rotate_q = 1;
   p.is_neox = desc->is_neox_style ? 1 : 0;
   p.scale_log2 = scale_log2_of(desc->head_dim);
+  p.pg = pg;
   p.chunk = pick_chunk(desc->batch, desc->n_kv_heads, desc->total_kv_len, max_kv_len);
   p.max_splits = (max_kv_len + p.chunk - 1) / p.chunk;
   if (p.max_splits > 1) {
@@ -541,6 +580,24 @@ int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial
   g_launches += launches;
   if (e != cudaSuccess) return cuda_fail(e, "decode attention launch");
   return GPU_OPS_OK;
+}
+
+int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial, float *lse_partial,
+                          const void *q_in, const void *k_in, const void *v_in, void *k_cache, void *v_cache,
+                          const void *freqs_cis_dev, const int32_t *kv_len_dev, const int32_t *rope_pos_dev,
+                          int append_new, int max_kv_len, void *workspace, size_t workspace_bytes,
+                          gpu_stream_t stream) {
+  return decode_common(desc, nullptr, out, o_partial, lse_partial, q_in, k_in, v_in, k_cache, v_cache, freqs_cis_dev,
+                       kv_len_dev, rope_pos_dev, append_new, max_kv_len, workspace, workspace_bytes, stream);
+}
+
+int gpu_attn_decode_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out, const void *q_in,
+                                const void *k_in, const void *v_in, void *k_pool, void *v_pool,
+                                const void *freqs_cis_dev, const int32_t *kv_len_dev, int append_new, int max_kv_len,
+                                void *workspace, size_t workspace_bytes, gpu_stream_t stream) {
+  if (!pages) return fail(GPU_OPS_E_INVALID, "null page description");
+  return decode_common(desc, pages, out, nullptr, nullptr, q_in, k_in, v_in, k_pool, v_pool, freqs_cis_dev, kv_len_dev,
+                       nullptr, append_new, max_kv_len, workspace, workspace_bytes, stream);
 }
 
 static int merge_parts(void *out, const float *o_parts, const float *lse_parts, long stride_o, long stride_lse,

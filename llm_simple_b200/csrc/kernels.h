@@ -10,6 +10,20 @@ namespace b200attn {
 // Record the message gpu_ops_last_error_string() returns on the calling thread.
 void set_last_error(const char *msg);
 
+// ---- paged KV cache --------------------------------------------------------
+// Optional indirection of cache positions: with table != nullptr, position pos of
+// sequence b lives in page table[b * table_stride + (pos >> page_shift)] of a pool of
+// pages page_stride elements apart, at in-page position pos & ((1 << page_shift) - 1);
+// the geometry's head / position strides then address inside a page and its sequence
+// stride is not used.  Pages hold a power of two >= 64 positions, so that a tile of 64
+// (decode) never straddles two pages.
+struct KvPaging {
+  const int32_t *table;
+  long page_stride;
+  int table_stride;
+  int page_shift;
+};
+
 // ---- RoPE + append ---------------------------------------------------------
 // One of up to three tensors handled by a rope_append launch (Q, K, V).
 struct RopeStream {
@@ -30,6 +44,7 @@ struct RopeParams {
   int start_pos;
   int batch, m, slots; // slots = sum of heads
   int is_neox;
+  KvPaging pg;         // applies to the streams with dst_at_pos
 };
 
 cudaError_t launch_rope_append(const RopeParams &p, bool bf16, cudaStream_t stream);
@@ -68,6 +83,7 @@ struct DecodeParams {
   float *ws_o;          // [rows][max_splits][128] fp32, rows = batch*m*H
   float *ws_lse;        // [rows][max_splits] (log2 domain)
   float scale_log2;
+  KvPaging pg;
 };
 
 cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t stream, int *launches);

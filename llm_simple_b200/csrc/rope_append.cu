@@ -57,8 +57,16 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeParams p) {
     const RopeStream &st = p.s[which];
     const int start = p.start_pos_dev ? p.start_pos_dev[b] : p.start_pos;
     const T *src = static_cast<const T *>(st.src) + b * st.src_seq + t * st.src_tok + slot * kHeadDim;
-    T *dst = static_cast<T *>(st.dst) + b * st.dst_seq + (t + (st.dst_at_pos ? start : 0)) * st.dst_tok +
-             slot * st.dst_head;
+    T *dst;
+    if (st.dst_at_pos && p.pg.table) {
+      const int pos = start + t;
+      const long page = p.pg.table[static_cast<long>(b) * p.pg.table_stride + (pos >> p.pg.page_shift)];
+      dst = static_cast<T *>(st.dst) + page * p.pg.page_stride + (pos & ((1 << p.pg.page_shift) - 1)) * st.dst_tok +
+            slot * st.dst_head;
+    } else {
+      dst = static_cast<T *>(st.dst) + b * st.dst_seq + (t + (st.dst_at_pos ? start : 0)) * st.dst_tok +
+            slot * st.dst_head;
+    }
     const int c0 = (st.rotate && !p.is_neox) ? 2 * i : i;
     const int c1 = (st.rotate && !p.is_neox) ? 2 * i + 1 : i + 8;
     uint4 u0 = *reinterpret_cast<const uint4 *>(src + c0 * 8);
