@@ -387,6 +387,9 @@ def main():
         line["e2e"] = e2e_leg(torch, ops, args, cfg, desc, lens, lens_d, k_cache, v_cache, table, ws, ws_bytes,
                               max_kv, H_l, kvh_l, world, dev, barrier, bytes_layer_all)
         line["prefill"] = prefill_leg(torch, ops, orc, world, dev, barrier, pk)
+        if world == 1:
+            line["paged_decode"] = paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, kvh_l, dev,
+                                             pk)
         if rank == 0 and world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, lens)
     if rank == 0:
@@ -466,6 +469,49 @@ def e2e_leg(torch, ops, args, cfg, desc, lens, lens_d, k_cache, v_cache, table, 
     for o in objs:
         o.close()
     return res
+
+
+def paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, kvh_l, dev, pk, layers=4, page_size=256):
+    """The decode step over a PAGED cache (pages of 256 positions handed out in random
+    order), on `layers` layers with caches of their own: the same kernel, the page table
+    looked up once per tile of 64 positions."""
+    batch = cfg["batch"]
+    per_seq = (cfg["len_hi"] + 8 + page_size - 1) // page_size
+    n_pages = batch * per_seq
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(cfg["seed"] + 77)
+    tbl = torch.randperm(n_pages, generator=gen, device=dev).to(torch.int32).reshape(batch, per_seq)
+    pools = [(torch.empty((n_pages, kvh_l, page_size, D), dtype=torch.bfloat16, device=dev).normal_(generator=gen),
+              torch.empty((n_pages, kvh_l, page_size, D), dtype=torch.bfloat16, device=dev).normal_(generator=gen))
+             for _ in range(layers)]
+    q = torch.empty((layers, batch, H_l * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    k = torch.empty((layers, batch, kvh_l * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    v = torch.empty((layers, batch, kvh_l * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    out = torch.empty((layers, batch, H_l * D), dtype=torch.bfloat16, device=dev)
+    desc = ops.make_desc(DT_BF16, batch, H_l, kvh_l, 1, page_size, layout="head", is_neox=cfg["neox"])
+    desc.total_kv_len = sum(L + 1 for L in lens)
+    pages = ops.make_pages(tbl, page_size, kvh_l * page_size * D)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for l in range(layers):
+            ops.gpu_attn_decode_paged_layer(desc, pages, out[l], q[l], k[l], v[l], pools[l][0], pools[l][1], table,
+                                            lens_d, True, max_kv, ws, ws_bytes, stream=stream)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    e0.record(stream)
+    for _ in range(reps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms_layer = e0.elapsed_time(e1) / (reps * layers)
+    gbs = decode_bytes([L + 1 for L in lens], H_l, kvh_l) / (ms_layer * 1e-3) / 1e9
+    return {"value": gbs, "unit": "GB/s", "ms_per_layer": ms_layer, "page_size": page_size, "layers": layers,
+            "frac_of_hbm_peak": gbs / pk["hbm"],
+            "l2": "four layers' pools, 2.8 GB, cycled: inputs larger than L2"}
 
 
 def prefill_leg(torch, ops, orc, world, dev, barrier, pk):

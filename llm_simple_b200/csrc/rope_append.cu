@@ -69,12 +69,13 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeParams p) {
     }
     const int c0 = (st.rotate && !p.is_neox) ? 2 * i : i;
     const int c1 = (st.rotate && !p.is_neox) ? 2 * i + 1 : i + 8;
-    uint4 u0 = *reinterpret_cast<const uint4 *>(src + c0 * 8);
-    uint4 u1 = *reinterpret_cast<const uint4 *>(src + c1 * 8);
+    // the tensors stream through once: keep them from evicting the table and bias rows in L1
+    uint4 u0 = __ldcs(reinterpret_cast<const uint4 *>(src + c0 * 8));
+    uint4 u1 = __ldcs(reinterpret_cast<const uint4 *>(src + c1 * 8));
     if (st.bias) {
       const T *bias = static_cast<const T *>(st.bias) + slot * kHeadDim;
-      add_bias_chunk<T>(u0, *reinterpret_cast<const uint4 *>(bias + c0 * 8));
-      add_bias_chunk<T>(u1, *reinterpret_cast<const uint4 *>(bias + c1 * 8));
+      add_bias_chunk<T>(u0, __ldg(reinterpret_cast<const uint4 *>(bias + c0 * 8)));
+      add_bias_chunk<T>(u1, __ldg(reinterpret_cast<const uint4 *>(bias + c1 * 8)));
     }
     if (st.rotate) {
       const float4 *tab = reinterpret_cast<const float4 *>(p.freqs_cis + (static_cast<long>(start) + t) * kHeadDim + 16 * i);
