@@ -490,7 +490,7 @@ def paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, k
     out = torch.empty((layers, batch, H_l * D), dtype=torch.bfloat16, device=dev)
     desc = ops.make_desc(DT_BF16, batch, H_l, kvh_l, 1, page_size, layout="head", is_neox=cfg["neox"])
     desc.total_kv_len = sum(L + 1 for L in lens)
-    pages = ops.make_pages(tbl, page_size, kvh_l * page_size * D)
+    pages = ops.make_pages(tbl, page_size, kvh_l * page_size * D, n_pages)
     stream = torch.cuda.current_stream()
 
     def step():

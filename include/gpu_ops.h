@@ -245,6 +245,8 @@ typedef struct gpu_kv_pages {
   int32_t table_stride;
   int32_t page_size;
   int64_t page_stride;       /* elements between consecutive pages of the pool */
+  int32_t n_pages;           /* pages in the pool (every table entry the call uses is below it) */
+  int32_t reserved;          /* 0 */
 } gpu_kv_pages;
 
 /* gpu_rope_kv_append_layer writing K and V through the page table. */
@@ -253,6 +255,13 @@ int gpu_rope_kv_append_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages
                                    const void *k_in, const void *v_in, const void *freqs_cis_dev,
                                    const int32_t *start_pos_dev, int start_pos, int m,
                                    gpu_stream_t stream);
+
+/* gpu_attn_prefill_layer over a paged cache.  The tcgen05 kernel reads K and V in
+ * tiles of 128 positions and so needs pages of at least 128; smaller pages run
+ * on the mma.sync kernel. */
+int gpu_attn_prefill_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out,
+                                 const void *q, const void *k_pool, const void *v_pool, int m,
+                                 int offset, gpu_stream_t stream);
 
 /* gpu_attn_decode_layer over a paged cache (final output only; same workspace
  * sizing, same split and merge kernels; the page of position kv_len[b] must be

@@ -313,20 +313,28 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_mma_kernel(PrefillParams 
   const int ntiles = (kv_end + kTileN - 1) / kTileN;
 
   const T *qbase = static_cast<const T *>(p.q) + b * p.g.q_seq + h * kHeadDim;
-  const T *kbase = static_cast<const T *>(p.k_cache) + b * p.g.c_seq + kvh * p.g.c_head;
-  const T *vbase = static_cast<const T *>(p.v_cache) + b * p.g.c_seq + kvh * p.g.c_head;
+  // flat cache: the sequence's block; paged cache: the pool, one page lookup per tile of 64
+  const bool paged = p.pg.table != nullptr;
+  const int32_t *ptab = paged ? p.pg.table + static_cast<long>(b) * p.pg.table_stride : nullptr;
+  const long seq_off = paged ? 0 : b * p.g.c_seq;
+  const T *kbase = static_cast<const T *>(p.k_cache) + seq_off + kvh * p.g.c_head;
+  const T *vbase = static_cast<const T *>(p.v_cache) + seq_off + kvh * p.g.c_head;
 
   auto load_tile = [&](int t) {
     const int tpos = t * kTileN;
     const uint32_t ks = smem_u32(stage_s + (t & 1) * 2 * kTileBytes);
     const uint32_t vs = ks + kTileBytes;
+    long tile_off = static_cast<long>(tpos) * p.g.c_pos;
+    if (paged && tpos < kv_end)
+      tile_off = static_cast<long>(ptab[tpos >> p.pg.page_shift]) * p.pg.page_stride +
+                 static_cast<long>(tpos & ((1 << p.pg.page_shift) - 1)) * p.g.c_pos;
 #pragma unroll
     for (int it = 0; it < kTileN * 16 / 128; ++it) {
       const int cidx = tid + it * 128;
       const int row = cidx >> 4, chunk = cidx & 15;
       const int pos = tpos + row;
       const bool valid = pos < kv_end;
-      const long off = valid ? pos * p.g.c_pos + chunk * 8 : 0;
+      const long off = valid ? tile_off + row * p.g.c_pos + chunk * 8 : 0;
       cp_async16(ks + swz_off(row, chunk), kbase + off, valid ? 16 : 0);
       cp_async16(vs + swz_off(row, chunk), vbase + off, valid ? 16 : 0);
     }

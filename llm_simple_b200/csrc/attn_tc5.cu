@@ -217,6 +217,9 @@ struct Params {
   long out_seq, out_tok;
   float scale_log2;
   int *error_flag;
+  // paged cache: page id of (sequence b, position pos) = page_table[b * table_stride + (pos >> page_shift)]
+  const int32_t *page_table;
+  int table_stride, page_shift;
 };
 
 template <int R> __device__ __forceinline__ void reg_dec() {
@@ -229,7 +232,8 @@ template <int R> __device__ __forceinline__ void reg_inc() {
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, Params p) {
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k_tail,
+                        const __grid_constant__ CUtensorMap map_v_tail, Params p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -290,14 +294,29 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
+        // Flat cache: coordinates (d, position, kv head, sequence); rows at and beyond n are
+        // outside the map and read as zero.  Paged cache: (d, position in page, kv head, page);
+        // the page that holds position n - 1 is read through a second map that ends at that
+        // position, so that the unwritten rest of the page reads as zero too.
+        int c1 = j * kBN, c3 = b;
+        const CUtensorMap *mk = &map_k, *mv = &map_v;
+        if (p.page_table) {
+          const int pi = c1 >> p.page_shift;
+          c3 = p.page_table[static_cast<long>(b) * p.table_stride + pi];
+          c1 &= (1 << p.page_shift) - 1;
+          if (pi == ((p.n - 1) >> p.page_shift)) {
+            mk = &map_k_tail;
+            mv = &map_v_tail;
+          }
+        }
         if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) break;
         mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
-        tma_load_4d(smem_base + kSmemK + s * kTileBytes, &map_k, bar(BAR_KFULL + s), 0, j * kBN, kvh, b);
-        tma_load_4d(smem_base + kSmemK + s * kTileBytes + kHalfTile, &map_k, bar(BAR_KFULL + s), 64, j * kBN, kvh, b);
+        tma_load_4d(smem_base + kSmemK + s * kTileBytes, mk, bar(BAR_KFULL + s), 0, c1, kvh, c3);
+        tma_load_4d(smem_base + kSmemK + s * kTileBytes + kHalfTile, mk, bar(BAR_KFULL + s), 64, c1, kvh, c3);
         if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2)) break;
         mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
-        tma_load_4d(smem_base + kSmemV + s * kTileBytes, &map_v, bar(BAR_VFULL + s), 0, j * kBN, kvh, b);
-        tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, &map_v, bar(BAR_VFULL + s), 64, j * kBN, kvh, b);
+        tma_load_4d(smem_base + kSmemV + s * kTileBytes, mv, bar(BAR_VFULL + s), 0, c1, kvh, c3);
+        tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, mv, bar(BAR_VFULL + s), 64, c1, kvh, c3);
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- MMA issuer
@@ -558,12 +577,26 @@ int attn_tc5_error_status() {
 cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream) {
   using namespace tc5;
   const AttnGeom &g = p.g;
-  CUtensorMap mq, mk, mv;
-  // q: (d, head, token, seq); k/v: (d, pos, kv_head, seq)
-  if (!make_map(&mq, bf16, p.q, g.n_heads, p.m, g.batch, kHeadDim, g.q_tok, g.q_seq, 1, kBM) ||
-      !make_map(&mk, bf16, p.k_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1) ||
-      !make_map(&mv, bf16, p.v_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1))
-    return cudaErrorNotSupported;
+  CUtensorMap mq, mk, mv, mk_tail, mv_tail;
+  // q: (d, head, token, seq); k/v: (d, pos, kv_head, seq), or (d, pos in page, kv_head, page) over a pool
+  if (!make_map(&mq, bf16, p.q, g.n_heads, p.m, g.batch, kHeadDim, g.q_tok, g.q_seq, 1, kBM)) return cudaErrorNotSupported;
+  if (p.pg.table) {
+    const int page_size = 1 << p.pg.page_shift;
+    if (page_size < kBN) return cudaErrorNotSupported; // a K / V tile of 128 positions must lie inside one page
+    const uint64_t n_pages = static_cast<uint64_t>(p.pg.n_pages);
+    const uint64_t tail = static_cast<uint64_t>((p.n - 1) & (page_size - 1)) + 1;
+    if (!make_map(&mk, bf16, p.k_cache, page_size, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
+        !make_map(&mv, bf16, p.v_cache, page_size, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
+        !make_map(&mk_tail, bf16, p.k_cache, tail, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
+        !make_map(&mv_tail, bf16, p.v_cache, tail, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1))
+      return cudaErrorNotSupported;
+  } else {
+    if (!make_map(&mk, bf16, p.k_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1) ||
+        !make_map(&mv, bf16, p.v_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1))
+      return cudaErrorNotSupported;
+    mk_tail = mk;
+    mv_tail = mv;
+  }
   int *err = error_word();
   if (!err) return cudaErrorNotSupported;
   int *err_dev = nullptr;
@@ -578,16 +611,19 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   kp.out_tok = g.out_tok;
   kp.scale_log2 = p.scale_log2;
   kp.error_flag = err_dev;
+  kp.page_table = p.pg.table;
+  kp.table_stride = p.pg.table_stride;
+  kp.page_shift = p.pg.page_shift;
   dim3 grid((p.m + 2 * kBM - 1) / (2 * kBM), g.n_heads, g.batch);
   cudaError_t e;
   if (bf16) {
     e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return e;
-    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, kp);
+    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
   } else {
     e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return e;
-    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, kp);
+    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
   }
   return cudaGetLastError();
 }

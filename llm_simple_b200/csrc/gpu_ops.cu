@@ -266,12 +266,13 @@ int paging_from(const gpu_kv_pages *pages, KvPaging *pg) {
   if (!pages->page_table) return fail(GPU_OPS_E_INVALID, "null page table");
   const int ps = pages->page_size;
   if (ps < 64 || (ps & (ps - 1))) return fail(GPU_OPS_E_UNSUPPORTED, "page size %d: a power of two >= 64", ps);
-  if (pages->table_stride <= 0 || pages->page_stride <= 0 || pages->page_stride % 8)
-    return fail(GPU_OPS_E_INVALID, "table stride %d, page stride %lld", pages->table_stride,
-                static_cast<long long>(pages->page_stride));
+  if (pages->table_stride <= 0 || pages->page_stride <= 0 || pages->page_stride % 8 || pages->n_pages <= 0)
+    return fail(GPU_OPS_E_INVALID, "table stride %d, page stride %lld, pages %d", pages->table_stride,
+                static_cast<long long>(pages->page_stride), pages->n_pages);
   pg->table = pages->page_table;
   pg->page_stride = pages->page_stride;
   pg->table_stride = pages->table_stride;
+  pg->n_pages = pages->n_pages;
   int shift = 0;
   while ((1 << shift) < ps) ++shift;
   pg->page_shift = shift;
@@ -495,9 +496,11 @@ int gpu_bias_add_layer(void *output_dev, const void *input_dev, const void *bias
   return GPU_OPS_OK;
 }
 
-int gpu_attn_prefill_layer(const gpu_attn_desc *desc, void *out, const void *q, const void *k_cache,
-                           const void *v_cache, int m, int offset, gpu_stream_t stream) {
+static int prefill_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out, const void *q,
+                          const void *k_cache, const void *v_cache, int m, int offset, gpu_stream_t stream) {
   if (int rc = check_desc(desc)) return rc;
+  KvPaging pg;
+  if (int rc = paging_from(pages, &pg)) return rc;
   if (!out || !q || !k_cache || !v_cache) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
   if (m <= 0 || offset < 0) return fail(GPU_OPS_E_INVALID, "m %d, offset %d", m, offset);
   if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache))
@@ -512,7 +515,19 @@ int gpu_attn_prefill_layer(const gpu_attn_desc *desc, void *out, const void *q, 
   p.n = offset + m;
   p.offset = offset;
   p.scale_log2 = scale_log2_of(desc->head_dim);
+  p.pg = pg;
   return run_prefill(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+}
+
+int gpu_attn_prefill_layer(const gpu_attn_desc *desc, void *out, const void *q, const void *k_cache,
+                           const void *v_cache, int m, int offset, gpu_stream_t stream) {
+  return prefill_common(desc, nullptr, out, q, k_cache, v_cache, m, offset, stream);
+}
+
+int gpu_attn_prefill_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out, const void *q,
+                                 const void *k_pool, const void *v_pool, int m, int offset, gpu_stream_t stream) {
+  if (!pages) return fail(GPU_OPS_E_INVALID, "null page description");
+  return prefill_common(desc, pages, out, q, k_pool, v_pool, m, offset, stream);
 }
 
 size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len) {

@@ -22,6 +22,7 @@ struct KvPaging {
   long page_stride;
   int table_stride;
   int page_shift;
+  int n_pages; // pages in the pool
 };
 
 // ---- RoPE + append ---------------------------------------------------------
@@ -119,6 +120,7 @@ struct PrefillParams {
   const void *v_cache;
   int m, n, offset;
   float scale_log2;
+  KvPaging pg;    // tcgen05 kernel: pages of at least 128 positions
 };
 
 cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStream_t stream);

@@ -22,7 +22,7 @@ EXPORTS = [
     "gpu_rope_layer", "gpu_rope_single_layer", "gpu_split_qkv_layer", "gpu_rope_kv_append_layer",
     "gpu_qkv_rope_kv_append_layer", "gpu_bias_add_layer", "gpu_attn_prefill_layer",
     "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_rope_kv_append_paged_layer",
-    "gpu_attn_decode_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
+    "gpu_attn_decode_paged_layer", "gpu_attn_prefill_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
 ]
@@ -35,16 +35,17 @@ class GpuOpsError(RuntimeError):
 class KvPages(ctypes.Structure):
     """struct gpu_kv_pages (include/gpu_ops.h): page table of a paged KV cache."""
     _fields_ = [("page_table", ctypes.c_void_p), ("table_stride", ctypes.c_int32), ("page_size", ctypes.c_int32),
-                ("page_stride", ctypes.c_int64)]
+                ("page_stride", ctypes.c_int64), ("n_pages", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
-def make_pages(page_table, page_size, page_stride):
-    """page_table: device int32 tensor [batch][entries]; page_stride in elements."""
+def make_pages(page_table, page_size, page_stride, n_pages):
+    """page_table: device int32 tensor [batch][entries]; page_stride in elements; n_pages in the pool."""
     pg = KvPages()
     pg.page_table = _ptr(page_table)
     pg.table_stride = page_table.shape[1]
     pg.page_size = page_size
     pg.page_stride = page_stride
+    pg.n_pages = n_pages
     pg._keep = page_table
     return pg
 
@@ -108,6 +109,7 @@ def lib():
         L.gpu_attn_prefill_layer.argtypes = [dp] + [vp] * 4 + [i, i, vp]
         pp = ctypes.POINTER(KvPages)
         L.gpu_rope_kv_append_paged_layer.argtypes = [dp, pp] + [vp] * 7 + [i32p, i, i, vp]
+        L.gpu_attn_prefill_paged_layer.argtypes = [dp, pp] + [vp] * 4 + [i, i, vp]
         L.gpu_attn_decode_paged_layer.argtypes = [dp, pp] + [vp] * 7 + [i32p, i, i, vp, ctypes.c_size_t, vp]
         L.gpu_attn_decode_layer.argtypes = [dp, vp, f32p, f32p] + [vp] * 6 + [i32p, i32p, i, i, vp,
                                                                                ctypes.c_size_t, vp]
@@ -208,6 +210,11 @@ def gpu_rope_kv_append_paged_layer(desc, pages, q_out, k_pool, v_pool, q_in, k_i
     _check(lib().gpu_rope_kv_append_paged_layer(ctypes.byref(desc), ctypes.byref(pages), _ptr(q_out), _ptr(k_pool),
                                                 _ptr(v_pool), _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(freqs_cis),
                                                 _ptr(start_pos_dev), start_pos, m, _stream(stream)))
+
+
+def gpu_attn_prefill_paged_layer(desc, pages, out, q, k_pool, v_pool, m, offset, stream=None):
+    _check(lib().gpu_attn_prefill_paged_layer(ctypes.byref(desc), ctypes.byref(pages), _ptr(out), _ptr(q), _ptr(k_pool),
+                                              _ptr(v_pool), m, offset, _stream(stream)))
 
 
 def gpu_attn_decode_paged_layer(desc, pages, out, q_in, k_in, v_in, k_pool, v_pool, freqs_cis, kv_len_dev, append_new,

@@ -55,7 +55,7 @@ def test_paged_append_then_decode_matches_flat(ops, dt, neox, theta, page_size, 
     v_flat = dev(np.full((batch, kvh, max_pos, D), canary, np.uint16), dt)
     tab = orc.init_freq_cis(D, max_pos, theta, dt)
     tab_d = torch.from_numpy(tab).cuda()
-    pages = ops.make_pages(table, page_size, kvh * page_size * D)
+    pages = ops.make_pages(table, page_size, kvh * page_size * D, n_pages)
     # ---- prompts: every sequence appends m rows at position 0 (rows beyond its length are overwritten later)
     m = int(lens.max())
     q = rnd_bits((batch, m, H * D), dt, 1)
@@ -103,6 +103,58 @@ def test_paged_append_then_decode_matches_flat(ops, dt, neox, theta, page_size, 
     assert np.array_equal(got_k, host(k_flat))           # the appended rows landed in the right pages
 
 
+@pytest.mark.parametrize("dt", [FP16, BF16])
+@pytest.mark.parametrize("page_size,kernel", [(64, 0), (128, 2), (256, 2), (128, 1)])
+def test_paged_chunked_prefill_matches_flat(ops, dt, page_size, kernel):
+    """Two prefill chunks (offset 0, then offset m1) over a paged cache whose never-written rows hold
+    NaN: the output equals the flat-cache output bit for bit and the NaN rows are never seen.
+    kernel 0 = automatic choice (pages of 64 run on the mma.sync kernel), 1 = mma.sync, 2 = tcgen05."""
+    batch, H, kvh, m1, m2, max_pos = 2, 8, 2, 200, 130, 512
+    nan = np.uint16(0x7E00 if dt == FP16 else 0x7FC0)
+    table_np, n_pages = _tables(batch, max_pos, page_size, 5)
+    table = torch.from_numpy(table_np).cuda()
+    k_pool = dev(np.full((n_pages, kvh, page_size, D), nan, np.uint16), dt)
+    v_pool = dev(np.full((n_pages, kvh, page_size, D), nan, np.uint16), dt)
+    k_flat = dev(np.full((batch, kvh, max_pos, D), nan, np.uint16), dt)
+    v_flat = dev(np.full((batch, kvh, max_pos, D), nan, np.uint16), dt)
+    tab = orc.init_freq_cis(D, max_pos, 1e4, dt)
+    tab_d = torch.from_numpy(tab).cuda()
+    pages = ops.make_pages(table, page_size, kvh * page_size * D, n_pages)
+    # the flat reference runs on the kernel the paged call will end up on
+    flat_kernel = 1 if (kernel == 1 or page_size < 128) else 2
+    try:
+        off = 0
+        for c, m in enumerate((m1, m2)):
+            q = rnd_bits((batch, m, H * D), dt, 100 + c)
+            k, v = rnd_bits((batch, m, kvh * D), dt, 110 + c), rnd_bits((batch, m, kvh * D), dt, 120 + c)
+            d_flat = ops.make_desc(dt, batch, H, kvh, m, max_pos, layout="head")
+            d_page = ops.make_desc(dt, batch, H, kvh, m, page_size, layout="head")
+            qe_a = torch.empty((batch, m, H * D), dtype=k_pool.dtype, device="cuda")
+            qe_b = torch.empty_like(qe_a)
+            o_a, o_b = torch.empty_like(qe_a), torch.empty_like(qe_a)
+            ops.gpu_rope_kv_append_layer(d_flat, qe_a, k_flat, v_flat, dev(q, dt), dev(k, dt), dev(v, dt), tab_d, None,
+                                         off, m)
+            ops.gpu_attn_set_prefill_kernel(flat_kernel)
+            ops.gpu_attn_prefill_layer(d_flat, o_a, qe_a, k_flat, v_flat, m, off)
+            ops.gpu_attn_set_prefill_kernel(kernel)
+            ops.gpu_rope_kv_append_paged_layer(d_page, pages, qe_b, k_pool, v_pool, dev(q, dt), dev(k, dt), dev(v, dt),
+                                               tab_d, None, off, m)
+            ops.gpu_attn_prefill_paged_layer(d_page, pages, o_b, qe_b, k_pool, v_pool, m, off)
+            torch.cuda.synchronize()
+            assert ops.gpu_ops_kernel_status() == 0
+            assert bool(torch.isfinite(o_b.float()).all()), "chunk %d reads unwritten rows" % c
+            assert torch.equal(o_a.view(torch.int16), o_b.view(torch.int16)), "chunk %d" % c
+            off += m
+        # against the oracle: sequence 1, second chunk
+        b, n = 1, m1 + m2
+        kc = host(k_flat)[b, :, :n].transpose(1, 0, 2).reshape(n, kvh * D).copy()
+        vc = host(v_flat)[b, :, :n].transpose(1, 0, 2).reshape(n, kvh * D).copy()
+        gold = orc.attn(host(qe_b)[b], kc, vc, m2, n, m1, H // kvh, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
+        assert_parity(host(o_b)[b], gold, dt, "paged prefill vs oracle")
+    finally:
+        ops.gpu_attn_set_prefill_kernel(0)
+
+
 def test_paged_rejects_bad_page_description(ops):
     desc = ops.make_desc(FP16, 1, 4, 2, 1, 64)
     t = torch.zeros((1, 4), dtype=torch.int32, device="cuda")
@@ -111,6 +163,6 @@ def test_paged_rejects_bad_page_description(ops):
     lens = torch.zeros(1, dtype=torch.int32, device="cuda")
     for size in (48, 32, 96):
         with pytest.raises(ops.GpuOpsError):
-            ops.gpu_attn_decode_paged_layer(desc, ops.make_pages(t, size, 2 * 64 * 128), x, x, x, x, x, x, tab, lens,
+            ops.gpu_attn_decode_paged_layer(desc, ops.make_pages(t, size, 2 * 64 * 128, 4), x, x, x, x, x, x, tab, lens,
                                             True, 1, None, 0)
     assert "page size" in ops.last_error_string()
