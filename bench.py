@@ -80,11 +80,14 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.t_begin = self.t_end = None
 
-    def __enter__(self):
+    def start(self):
+        """Starts sampling (20 ms period).  Called before the warm-up, because the first sample
+        arrives about 0.1 s after the sampler starts and a timed region can be shorter than that."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -92,12 +95,20 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def __enter__(self):
+        if self.proc is None:
+            self.start()
+        self.t_begin = time.monotonic()
+        return self
+
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.monotonic(), [x.strip() for x in line.split(",")]))
 
     def __exit__(self, *a):
+        self.t_end = time.monotonic()
         if self.proc:
+            time.sleep(0.03)          # let a sample taken inside the region arrive
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -105,21 +116,34 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-            except (ValueError, IndexError):
-                continue
-            for i, n in enumerate(names):
-                if len(r) > 3 + i and r[3 + i].lower().startswith("active"):
-                    reasons.add(n)
+
+        def collect(lo, hi):
+            sm, mx, reasons = [], [], set()
+            for t, r in self.rows:
+                if t < lo or t > hi:
+                    continue
+                try:
+                    sm.append(float(r[0]))
+                    mx.append(float(r[1]))
+                except (ValueError, IndexError):
+                    continue
+                for i, n in enumerate(names):
+                    if len(r) > 3 + i and r[3 + i].lower().startswith("active"):
+                        reasons.add(n)
+            return sm, mx, reasons
+        window = "timed region"
+        sm, mx, reasons = collect(self.t_begin or 0.0, (self.t_end or 1e30) + 0.03)
+        if not sm:
+            # the region was shorter than the sampling period: the warm-up steps just before it ran
+            # the same launches back to back, so their samples show the same load
+            window = "warm-up and timed region (timed region shorter than the sampling period)"
+            sm, mx, reasons = collect(0.0, (self.t_end or 1e30) + 0.03)
+            sm, mx = sm[-5:], mx[-5:]
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 # ----------------------------------------------------------------------------
@@ -325,12 +349,24 @@ def main():
             def step():
                 graph.replay()
 
+    sampler = ClockSampler(local_rank).start()
+    t_warm = time.monotonic()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # extra untimed steps until the clock sampler has seen this load for a quarter of a second
+    # (the same count on every rank: the decision is rank 0's)
+    while True:
+        more = torch.tensor([1 if time.monotonic() - t_warm < 0.25 else 0], device=dev)
+        if world > 1:
+            dist.broadcast(more, 0)
+        if not int(more.item()):
+            break
+        step()
+        barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ops.gpu_ops_launch_count(True)
-    with ClockSampler(local_rank) as clk:
+    with sampler as clk:
         barrier()
         ev0.record(stream)
         for _ in range(args.steps):
