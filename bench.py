@@ -47,6 +47,8 @@ CFG4 = dict(name="cfg4 Qwen2.5-14B-shaped batched GQA decode", layers=48, batch=
 # from the ncu capture summarised in profiles/attn_decode_kernel_cfg4_1layer.md (700.9 / 693.68 MB)
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 700.9 / 693.68
 CFG3 = dict(name="cfg3 Llama-2-13B-shaped causal prefill", batch=8, seq=2048, n_heads=40, theta=1e4, neox=False)
+CFG5 = dict(name="cfg5 Qwen2.5-32B-shaped chunked causal prefill", batch=1, seq=32768, chunk=4096, n_heads=40,
+            n_kv_heads=8, theta=1e6, neox=True)
 
 
 def peaks():
@@ -550,6 +552,59 @@ def paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, k
             "l2": "four layers' pools, 2.8 GB, cycled: inputs larger than L2"}
 
 
+def long_prefill_leg(torch, ops, orc, world, dev, barrier, pk, flush):
+    """cfg5, one layer: a 32768-token prompt prefilled in chunks of 4096 (RoPE + append of the
+    chunk, then causal attention of the chunk over everything cached so far), bf16, GQA 40/8,
+    KV heads sharded over the ranks.  10.995 TFLOP per layer over all ranks."""
+    import torch.distributed as dist
+    c = CFG5
+    if c["n_kv_heads"] % world:
+        return {"skipped": "KV heads do not divide"}
+    kvh_l = c["n_kv_heads"] // world
+    H_l = c["n_heads"] // world
+    S, m = c["seq"], c["chunk"]
+    max_pos = S + 128
+    desc = ops.make_desc(DT_BF16, 1, H_l, kvh_l, m, max_pos, layout="head", is_neox=c["neox"])
+    q = torch.randn((S // m, m, H_l * D), dtype=torch.bfloat16, device=dev)
+    k = torch.randn((S // m, m, kvh_l * D), dtype=torch.bfloat16, device=dev)
+    v = torch.randn_like(k)
+    qe = torch.empty((m, H_l * D), dtype=torch.bfloat16, device=dev)
+    o = torch.empty_like(qe)
+    kc = torch.zeros((1, kvh_l, max_pos, D), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    table = torch.from_numpy(orc.init_freq_cis(D, max_pos, c["theta"], orc.DT_BFLOAT16)).to(dev)
+    stream = torch.cuda.current_stream()
+
+    def layer_pass():
+        for ci in range(S // m):
+            ops.gpu_rope_kv_append_layer(desc, qe, kc, vc, q[ci], k[ci], v[ci], table, None, ci * m, m, stream=stream)
+            ops.gpu_attn_prefill_layer(desc, o, qe, kc, vc, m, ci * m, stream=stream)
+
+    for _ in range(2):
+        layer_pass()
+    times = []
+    for _ in range(5):
+        flush.zero_()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        layer_pass()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        times.append(ms)
+    ms = statistics.median(times)
+    fl = sum(prefill_flops(1, c["n_heads"], m, ci * m) for ci in range(S // m))
+    tf = fl / (ms * 1e-3) / 1e12
+    return {"workload": c["name"], "dtype": "bf16", "ms_per_layer": ms, "tflops": tf, "flops_per_layer": fl,
+            "per_rank_frac_of_tensor_peak": tf / world / pk["tensor"], "chunks": S // m,
+            "note": "layer pass: RoPE + append and attention of all 8 chunks; 256 MB L2 flush before each pass"}
+
+
 def prefill_leg(torch, ops, orc, world, dev, barrier, pk):
     """cfg3 prefill, one layer pass: fused RoPE + KV append, then causal attention."""
     import torch.distributed as dist
@@ -625,6 +680,7 @@ def prefill_leg(torch, ops, orc, world, dev, barrier, pk):
         ms = statistics.median(times)
         gbs = pass_bytes / (ms * 1e-3) / 1e9
         res[name] = {"ms": ms, "gbs": gbs, "bytes": pass_bytes, "frac_of_hbm_peak": gbs / pk["hbm"]}
+    res["cfg5_chunked_prefill"] = long_prefill_leg(torch, ops, orc, world, dev, barrier, pk, flush)
     per_rank = res["attention_only"]["tflops"] / world
     res.update({"workload": c["name"], "dtype": "fp16", "flops_per_layer": prefill_flops(batch, c["n_heads"], S, 0),
                 "l2": "256 MB flush between iterations",
