@@ -228,6 +228,41 @@ int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const vo
 size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len);
 
 /* ------------------------------------------------------------------------
+ * Cross-device split-KV decode: exchange and merge of the ranks' partials in
+ * ONE kernel over NVLink peer memory (plain peer stores, system-scope fence,
+ * flags; no collective library call).  The reference is single-device and has
+ * no counterpart.
+ *
+ * Every rank owns one exchange buffer of gpu_attn_xchg_buffer_bytes(world, rows)
+ * bytes, zero-filled, visible to its peers (gpu_peer_buffer_alloc / _open, CUDA
+ * IPC; one process per GPU).  Per decode step (epoch = 1, 2, 3, ... identical on
+ * all ranks): gpu_attn_decode_layer writes this rank's partial to
+ * gpu_attn_xchg_local_slot(...) (o_partial = the returned pointer, lse_partial =
+ * that + rows*head_dim), then gpu_attn_xchg_merge_layer copies it into every
+ * peer's buffer, waits (bounded: about a second, then gpu_ops_kernel_status()
+ * turns non-zero and the output is left unwritten) for the peers' partials of
+ * the same epoch and merges them: out [rows][head_dim], every rank gets the
+ * full result, bit-identical to all-gather + gpu_attn_merge_packed_layer.
+ * Consecutive epochs use the two halves of the buffer alternately; a rank may
+ * run at most one step ahead of its slowest peer, which the protocol enforces.
+ * ------------------------------------------------------------------------ */
+size_t gpu_attn_xchg_buffer_bytes(int world, int rows);
+float *gpu_attn_xchg_local_slot(void *local_buffer, int world, int rank, uint32_t epoch, int rows);
+/* peer_buffers: host array [world] of device addresses of the ranks' buffers as
+ * mapped in THIS process (entry [rank] is not used). */
+int gpu_attn_xchg_merge_layer(void *out, void *local_buffer, void *const *peer_buffers, int world,
+                              int rank, uint32_t epoch, int rows, int head_dim, int dt,
+                              gpu_stream_t stream);
+
+/* Device memory that other processes of the node can map: cudaMalloc + zero
+ * fill + IPC export (handle64: 64 bytes to hand to the peers), import, unmap,
+ * free.  Allocation helpers, not operators: call them at start-up. */
+int gpu_peer_buffer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+int gpu_peer_buffer_open(const unsigned char *handle64, void **ptr);
+int gpu_peer_buffer_close(void *ptr);
+int gpu_peer_buffer_free(void *ptr);
+
+/* ------------------------------------------------------------------------
  * Paged KV cache.  The reference allocates one flat block per layer
  * (src/llama2_layer_npu.cpp:1148-1149); for batched serving the cache is a
  * pool of fixed-size pages and a per-sequence page table instead.

@@ -569,6 +569,13 @@ int *error_word() {
 
 } // namespace tc5
 
+int *kernel_error_word_dev() {
+  int *w = tc5::error_word();
+  int *dev = nullptr;
+  if (!w || cudaHostGetDevicePointer(reinterpret_cast<void **>(&dev), w, 0) != cudaSuccess) return nullptr;
+  return dev;
+}
+
 int attn_tc5_error_status() {
   int *w = tc5::error_word();
   return w ? *reinterpret_cast<volatile int *>(w) : 0;

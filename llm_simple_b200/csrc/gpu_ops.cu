@@ -11,6 +11,7 @@
 #include <mutex>
 #include <string>
 #include <cstdlib>
+#include <cstring>
 
 using namespace b200attn;
 
@@ -653,6 +654,97 @@ int gpu_attn_merge_packed_layer(void *out, const float *parts, int n_parts, int 
   const long stride = static_cast<long>(rows) * (128 + 1);
   return merge_parts(out, parts, parts + static_cast<long>(rows) * 128, stride, stride, n_parts, rows, head_dim, dt,
                      stream);
+}
+
+// ---- cross-device exchange over peer memory ----------------------------------
+namespace {
+size_t align16(size_t x) { return (x + 15) & ~static_cast<size_t>(15); }
+size_t xchg_slots_bytes(int world, int rows) { return align16(static_cast<size_t>(world) * rows * 129 * 4); }
+size_t xchg_half_bytes(int world, int rows) { return xchg_slots_bytes(world, rows) + align16(static_cast<size_t>(world) * 4); }
+} // namespace
+
+size_t gpu_attn_xchg_buffer_bytes(int world, int rows) {
+  if (world <= 0 || rows <= 0) return 0;
+  return 2 * xchg_half_bytes(world, rows);
+}
+
+float *gpu_attn_xchg_local_slot(void *local_buffer, int world, int rank, uint32_t epoch, int rows) {
+  if (!local_buffer || world <= 0 || rank < 0 || rank >= world || rows <= 0) return nullptr;
+  char *half = static_cast<char *>(local_buffer) + (epoch & 1u) * xchg_half_bytes(world, rows);
+  return reinterpret_cast<float *>(half) + static_cast<size_t>(rank) * rows * 129;
+}
+
+int gpu_attn_xchg_merge_layer(void *out, void *local_buffer, void *const *peer_buffers, int world, int rank,
+                              uint32_t epoch, int rows, int head_dim, int dt, gpu_stream_t stream) {
+  if (int rc = check_common(dt, head_dim)) return rc;
+  if (!out || !local_buffer || !peer_buffers) return fail(GPU_OPS_E_INVALID, "null pointer");
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || rows <= 0 || epoch == 0)
+    return fail(GPU_OPS_E_INVALID, "world %d (1..%d), rank %d, rows %d, epoch %u", world, kMaxPeers, rank, rows, epoch);
+  XchgParams p{};
+  const size_t half = (epoch & 1u) * xchg_half_bytes(world, rows);
+  const size_t n = static_cast<size_t>(rows) * 129;
+  char *lb = static_cast<char *>(local_buffer) + half;
+  p.out = out;
+  p.slots = reinterpret_cast<const float *>(lb);
+  p.flags = reinterpret_cast<const uint32_t *>(lb + xchg_slots_bytes(world, rows));
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) continue;
+    if (!peer_buffers[r]) return fail(GPU_OPS_E_INVALID, "peer buffer %d is null", r);
+    char *pb = static_cast<char *>(peer_buffers[r]) + half;
+    p.peer_slot[r] = reinterpret_cast<float *>(pb) + static_cast<size_t>(rank) * n;
+    p.peer_flag[r] = reinterpret_cast<uint32_t *>(pb + xchg_slots_bytes(world, rows)) + rank;
+  }
+  p.epoch = epoch;
+  p.world = world;
+  p.rank = rank;
+  p.rows = rows;
+  p.error_flag = kernel_error_word_dev();
+  if (!p.error_flag) return fail(GPU_OPS_E_CUDA, "no status word");
+  cudaError_t e = launch_attn_xchg_merge(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "exchange + merge launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
+int gpu_peer_buffer_alloc(size_t bytes, void **ptr, unsigned char *handle64) {
+  if (!ptr || !handle64 || bytes == 0) return fail(GPU_OPS_E_INVALID, "null pointer or zero size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "peer buffer allocation");
+  if ((e = cudaMemset(p, 0, bytes)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "peer buffer clear");
+  }
+  cudaIpcMemHandle_t h;
+  if ((e = cudaIpcGetMemHandle(&h, p)) != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "peer buffer export");
+  }
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return GPU_OPS_OK;
+}
+
+int gpu_peer_buffer_open(const unsigned char *handle64, void **ptr) {
+  if (!ptr || !handle64) return fail(GPU_OPS_E_INVALID, "null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e, "peer buffer import");
+  return GPU_OPS_OK;
+}
+
+int gpu_peer_buffer_close(void *ptr) {
+  if (!ptr) return GPU_OPS_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? GPU_OPS_OK : cuda_fail(e, "peer buffer close");
+}
+
+int gpu_peer_buffer_free(void *ptr) {
+  if (!ptr) return GPU_OPS_OK;
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? GPU_OPS_OK : cuda_fail(e, "peer buffer free");
 }
 
 int gpu_ops_set_workspace(void *workspace, size_t bytes) {

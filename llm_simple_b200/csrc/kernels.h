@@ -128,7 +128,23 @@ cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStrea
 // tcgen05 / TMEM / TMA kernel; same contract.  Returns cudaErrorNotSupported if
 // the geometry cannot be described by its tensor maps.
 cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream);
-// Non-zero once a bounded wait inside a tcgen05 kernel on the current device has given up.
+// Non-zero once a bounded wait inside a kernel on the current device has given up.
 int attn_tc5_error_status();
+// Device address of that status word (host-mapped), or nullptr.
+int *kernel_error_word_dev();
+
+// ---- cross-device (O, LSE) exchange + merge over peer memory ------------------
+constexpr int kMaxPeers = 8;
+struct XchgParams {
+  void *out;                      // dtype [rows][128]
+  const float *slots;             // local buffer half of this step: [world][rows*129] fp32
+  const uint32_t *flags;          // local flags of this step's half: [world]
+  float *peer_slot[kMaxPeers];    // this rank's slot inside peer p's buffer half
+  uint32_t *peer_flag[kMaxPeers]; // this rank's flag inside peer p's buffer half
+  uint32_t epoch;                 // step counter, never 0
+  int world, rank, rows;
+  int *error_flag;
+};
+cudaError_t launch_attn_xchg_merge(const XchgParams &p, bool bf16, cudaStream_t stream);
 
 } // namespace b200attn

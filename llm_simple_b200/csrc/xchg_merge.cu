@@ -1,0 +1,105 @@
+// Cross-device merge of split-KV decode partials over NVLink peer memory.
+//
+// When a very long cache is sharded by position over the GPUs of a node, every
+// rank ends its decode step with a normalised partial output and its
+// log-sum-exp per query head (20 KB for 40 heads), and every rank needs all of
+// them.  Instead of a collective library call between two kernels, ONE kernel per
+// rank does the exchange and the merge:
+//   push blocks  (one per peer)  copy this rank's partial into its slot of the
+//                peer's exchange buffer with plain stores over NVLink, fence at
+//                system scope and release a flag there;
+//   merge blocks (one per query row) wait until every peer's flag in the LOCAL
+//                buffer shows this step, then merge the slots from local memory
+//                (same arithmetic and order as attn_merge_kernel, so the result
+//                is bit-identical to the collective-based path).
+// Peer buffers are ordinary device allocations opened through CUDA IPC; no
+// multimem, no TMA.  The two kinds of block never wait on each other, and a
+// waiting block only waits for kernels on OTHER GPUs.  Every wait is bounded
+// (about a second): on expiry the block records an error code in the host-mapped
+// status word and finishes.
+//
+// Buffer of one rank (floats / words), two halves used alternately by
+// consecutive steps so that a fast peer cannot overwrite a slot that is still
+// being merged:  half h: slots [world][rows*129] fp32, then flags [world] u32.
+// There is no counterpart in the reference, which is single-device.
+#include "kernels.h"
+#include "common.cuh"
+
+namespace b200attn {
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+} // namespace
+
+// grid: (world - 1) push blocks, then `rows` merge blocks; block: 128 threads
+template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_kernel(XchgParams p) {
+  const int tid = threadIdx.x;
+  const long n = static_cast<long>(p.rows) * (kHeadDim + 1);
+  if (static_cast<int>(blockIdx.x) < p.world - 1) {
+    // ---- push: this rank's slot -> the same slot in one peer's buffer
+    const int peer = static_cast<int>(blockIdx.x) < p.rank ? blockIdx.x : blockIdx.x + 1;
+    const float *src = p.slots + static_cast<long>(p.rank) * n;
+    float *dst = p.peer_slot[peer];
+    for (long i = tid; i < n; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) st_release_sys(p.peer_flag[peer], p.epoch);
+    return;
+  }
+  // ---- merge: wait for every peer's partial of this step, then combine
+  const int row = blockIdx.x - (p.world - 1), d = tid;
+  __shared__ int s_ok;
+  if (tid == 0) {
+    int ok = 1;
+    const long long t0 = clock64();
+    for (int r = 0; r < p.world && ok; ++r) {
+      if (r == p.rank) continue;
+      while (ld_acquire_sys(p.flags + r) != p.epoch) {
+        if (clock64() - t0 > 2000000000LL) {
+          *reinterpret_cast<volatile int *>(p.error_flag) = 20 + r; // gave up waiting for rank r
+          ok = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return; // the output row stays unwritten; the host sees the status word
+  // the slots were written by other GPUs: read them around L1
+  auto lse_at = [&](int i) { return __ldcg(p.slots + i * n + static_cast<long>(p.rows) * kHeadDim + row); };
+  auto o_at = [&](int i) { return __ldcg(p.slots + i * n + static_cast<long>(row) * kHeadDim + d); };
+  float M = -INFINITY;
+  for (int i = 0; i < p.world; ++i) M = fmaxf(M, lse_at(i) * kLog2e);
+  float W = 0.f, o = 0.f;
+  if (M != -INFINITY) {
+    for (int i = 0; i < p.world; ++i) {
+      const float w = exp2f(lse_at(i) * kLog2e - M);
+      W += w;
+      o += w * o_at(i);
+    }
+  }
+  const float res = (W > 0.f) ? o / W : 0.f;
+  static_cast<T *>(p.out)[static_cast<long>(row) * kHeadDim + d] = Elem<T>::from_f32(res);
+}
+
+cudaError_t launch_attn_xchg_merge(const XchgParams &p, bool bf16, cudaStream_t stream) {
+  const unsigned blocks = static_cast<unsigned>(p.world - 1 + p.rows);
+  if (bf16)
+    attn_xchg_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(p);
+  else
+    attn_xchg_merge_kernel<__half><<<blocks, 128, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+} // namespace b200attn

@@ -23,6 +23,8 @@ EXPORTS = [
     "gpu_qkv_rope_kv_append_layer", "gpu_bias_add_layer", "gpu_attn_prefill_layer",
     "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_rope_kv_append_paged_layer",
     "gpu_attn_decode_paged_layer", "gpu_attn_prefill_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
+    "gpu_attn_xchg_buffer_bytes", "gpu_attn_xchg_local_slot", "gpu_attn_xchg_merge_layer",
+    "gpu_peer_buffer_alloc", "gpu_peer_buffer_open", "gpu_peer_buffer_close", "gpu_peer_buffer_free",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
 ]
@@ -118,6 +120,15 @@ def lib():
         L.gpu_attn_decode_workspace_bytes.restype = ctypes.c_size_t
         L.gpu_attn_merge_lse_layer.argtypes = [vp, f32p, f32p, i, i, i, i, vp]
         L.gpu_attn_merge_packed_layer.argtypes = [vp, f32p, i, i, i, i, vp]
+        L.gpu_attn_xchg_buffer_bytes.argtypes = [i, i]
+        L.gpu_attn_xchg_buffer_bytes.restype = ctypes.c_size_t
+        L.gpu_attn_xchg_local_slot.argtypes = [vp, i, i, ctypes.c_uint32, i]
+        L.gpu_attn_xchg_local_slot.restype = vp
+        L.gpu_attn_xchg_merge_layer.argtypes = [vp, vp, ctypes.POINTER(vp), i, i, ctypes.c_uint32, i, i, i, vp]
+        L.gpu_peer_buffer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
+        L.gpu_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.gpu_peer_buffer_close.argtypes = [vp]
+        L.gpu_peer_buffer_free.argtypes = [vp]
         L.gpu_ops_set_workspace.argtypes = [vp, ctypes.c_size_t]
         L.gpu_attn_set_decode_chunk.argtypes = [i]
         L.gpu_attn_set_prefill_kernel.argtypes = [i]
@@ -253,6 +264,42 @@ def gpu_attn_decode_layer_noalloc(desc, out, q_in, k_in, v_in, k_cache, v_cache,
                                                _ptr(v_in), _ptr(k_cache), _ptr(v_cache), _ptr(freqs_cis),
                                                _ptr(kv_len_dev), _ptr(rope_pos_dev), int(bool(append_new)),
                                                max_kv_len, _stream(stream)))
+
+
+def gpu_peer_buffer_alloc(nbytes):
+    """-> (device address, 64-byte handle to hand to the other processes of the node)."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    _check(lib().gpu_peer_buffer_alloc(nbytes, ctypes.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def gpu_peer_buffer_open(handle):
+    ptr = ctypes.c_void_p()
+    _check(lib().gpu_peer_buffer_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def gpu_peer_buffer_close(ptr):
+    _check(lib().gpu_peer_buffer_close(ptr))
+
+
+def gpu_peer_buffer_free(ptr):
+    _check(lib().gpu_peer_buffer_free(ptr))
+
+
+def gpu_attn_xchg_buffer_bytes(world, rows):
+    return int(lib().gpu_attn_xchg_buffer_bytes(world, rows))
+
+
+def gpu_attn_xchg_local_slot(local_buffer, world, rank, epoch, rows):
+    return lib().gpu_attn_xchg_local_slot(local_buffer, world, rank, epoch, rows)
+
+
+def gpu_attn_xchg_merge_layer(out, local_buffer, peer_buffers, world, rank, epoch, rows, head_dim, dt, stream=None):
+    arr = (ctypes.c_void_p * world)(*[p for p in peer_buffers])
+    _check(lib().gpu_attn_xchg_merge_layer(_ptr(out), local_buffer, arr, world, rank, epoch, rows, head_dim, dt,
+                                           _stream(stream)))
 
 
 def gpu_attn_merge_lse_layer(out, o_parts, lse_parts, n_parts, rows, head_dim, dt, stream=None):

@@ -111,13 +111,56 @@ def _global_rank(dist, group, group_rank):
     return group_rank if group is None else dist.get_global_rank(group, group_rank)
 
 
+class PeerExchange:
+    """This rank's exchange buffer for the peer-memory (O, LSE) exchange, and its peers' buffers
+    mapped into this process (CUDA IPC; one process per GPU of one node).  The 64-byte handles
+    travel once, at construction, through the process group."""
+
+    def __init__(self, rows, group=None):
+        import torch.distributed as dist
+        from . import ops
+        self.ops, self.rows = ops, rows
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        nbytes = ops.gpu_attn_xchg_buffer_bytes(self.world, rows)
+        self.local, handle = ops.gpu_peer_buffer_alloc(nbytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.peers = [self.local if r == self.rank else ops.gpu_peer_buffer_open(handles[r])
+                      for r in range(self.world)]
+        self.epoch = 0
+        dist.barrier(group)          # every buffer exists and is zero before anyone pushes
+
+    def next_slot(self):
+        """Starts a step: returns the device address where this rank's packed partial of the step
+        belongs (rows*128 fp32 outputs, then rows log-sum-exps)."""
+        self.epoch += 1
+        return self.ops.gpu_attn_xchg_local_slot(self.local, self.world, self.rank, self.epoch, self.rows)
+
+    def merge(self, out, head_dim, dt, stream=None):
+        self.ops.gpu_attn_xchg_merge_layer(out, self.local, self.peers, self.world, self.rank, self.epoch, self.rows,
+                                           head_dim, dt, stream)
+
+    def close(self):
+        """Call on every rank, after a barrier that follows the last step."""
+        for r, p in enumerate(self.peers):
+            if r != self.rank and p:
+                self.ops.gpu_peer_buffer_close(p)
+        self.peers = []
+        if self.local:
+            self.ops.gpu_peer_buffer_free(self.local)
+            self.local = None
+
+
 class SplitKVDecoder:
     """Decode step over a cache sharded by position across the ranks of `group`.
 
     Each rank calls step() with its local slice of the cache; the result (all
     query heads, every rank gets the full output) is written to `out`."""
 
-    def __init__(self, desc, dt, group=None):
+    def __init__(self, desc, dt, group=None, exchange="nccl"):
+        """exchange: "nccl" = all-gather into local memory, then a merge kernel; "peer" = one kernel
+        per rank that pushes its partial into the peers' buffers over NVLink, waits for theirs and
+        merges (PeerExchange).  Both give the same bits."""
         import torch
         import torch.distributed as dist
         self.torch, self.dist = torch, dist
@@ -126,17 +169,32 @@ class SplitKVDecoder:
         self.rank = dist.get_rank(group)
         self.rows = desc.batch * desc.n_heads
         n = packed_partial_floats(self.rows, desc.head_dim)
-        self.send = torch.empty(n, dtype=torch.float32, device="cuda")
-        self.recv = torch.empty(self.world * n, dtype=torch.float32, device="cuda")
+        self.peer = None
+        if exchange == "peer":
+            self.peer = PeerExchange(self.rows, group)
+        elif exchange == "nccl":
+            self.send = torch.empty(n, dtype=torch.float32, device="cuda")
+            self.recv = torch.empty(self.world * n, dtype=torch.float32, device="cuda")
+        else:
+            raise ValueError("exchange must be 'nccl' or 'peer'")
 
     def step(self, out, q_in, k_in, v_in, k_cache, v_cache, freqs_cis, local_len_dev, rope_pos_dev, max_local_len,
              workspace, workspace_bytes):
         from . import ops
         tail = self.rank == self.world - 1
-        o_ptr = self.send.data_ptr()
+        o_ptr = self.peer.next_slot() if self.peer else self.send.data_ptr()
         lse_ptr = o_ptr + self.rows * self.desc.head_dim * 4
         ops.gpu_attn_decode_layer(self.desc, None, o_ptr, lse_ptr, q_in, k_in if tail else None,
                                   v_in if tail else None, k_cache, v_cache, freqs_cis, local_len_dev, rope_pos_dev,
                                   tail, max_local_len + (1 if tail else 0), workspace, workspace_bytes)
-        self.dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
-        ops.gpu_attn_merge_packed_layer(out, self.recv, self.world, self.rows, self.desc.head_dim, self.dt)
+        if self.peer:
+            self.peer.merge(out, self.desc.head_dim, self.dt)
+        else:
+            self.dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+            ops.gpu_attn_merge_packed_layer(out, self.recv, self.world, self.rows, self.desc.head_dim, self.dt)
+
+    def close(self):
+        if self.peer:
+            self.dist.barrier(self.group)
+            self.peer.close()
+            self.peer = None

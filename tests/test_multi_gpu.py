@@ -169,7 +169,20 @@ def _flow_rank(rank, world, port, ret):
                  torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
                  torch.tensor([prompt], dtype=torch.int32, device="cuda"), sl_hi - sl_lo, ws, ws_bytes)
         torch.cuda.synchronize()
-        ret[rank] = (host(k_dst[0, :, :sl_hi - sl_lo]), host(v_dst[0, :, :sl_hi - sl_lo]), host(out), host(out_p))
+        # ---- the same step with the exchange done by one kernel over peer memory: same bits, three
+        #      steps in a row (both halves of the exchange buffer; the tail rank rewrites the same row)
+        dec2 = sharding.SplitKVDecoder(desc_d, dt, exchange="peer")
+        same = True
+        for _ in range(3):
+            out2 = torch.zeros_like(out)
+            dec2.step(out2, dev(q[prompt:], dt), dev(k[prompt:], dt), dev(v[prompt:], dt), k_dst, v_dst, tab_d,
+                      torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
+                      torch.tensor([prompt], dtype=torch.int32, device="cuda"), sl_hi - sl_lo, ws, ws_bytes)
+            torch.cuda.synchronize()
+            same = same and torch.equal(out2.view(torch.int16), out.view(torch.int16))
+        same = same and ops.gpu_ops_kernel_status() == 0
+        dec2.close()
+        ret[rank] = (host(k_dst[0, :, :sl_hi - sl_lo]), host(v_dst[0, :, :sl_hi - sl_lo]), host(out), host(out_p), same)
     finally:
         dist.destroy_process_group()
 
@@ -189,7 +202,8 @@ def test_two_ranks_prefill_reshard_decode_flow():
                       threads=8).reshape(prompt, H, D)
     for r in range(world):
         lo, hi = sharding.position_slices(prompt, world)[r]
-        k_got, v_got, _, out_p = ret[r]
+        k_got, v_got, _, out_p, peer_same = ret[r]
+        assert peer_same, "peer-memory exchange differs from the all-gather path on rank %d" % r
         # the re-sharded slices hold exactly the rotated K and the raw V of their positions, all heads
         assert np.array_equal(k_got, k_rot[lo:hi].transpose(1, 0, 2))
         assert np.array_equal(v_got, v[lo:hi].reshape(hi - lo, kvh, D).transpose(1, 0, 2))
