@@ -425,6 +425,7 @@ def main():
         line["e2e"] = e2e_leg(torch, ops, args, cfg, desc, lens, lens_d, k_cache, v_cache, table, ws, ws_bytes,
                               max_kv, H_l, kvh_l, world, dev, barrier, bytes_layer_all)
         line["prefill"] = prefill_leg(torch, ops, orc, world, dev, barrier, pk)
+        line["cfg5_split_kv_decode"] = split_kv_leg(torch, ops, orc, world, rank, dev, barrier, pk)
         if world == 1:
             line["paged_decode"] = paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, kvh_l, dev,
                                              pk)
@@ -550,6 +551,77 @@ def paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, k
     return {"value": gbs, "unit": "GB/s", "ms_per_layer": ms_layer, "page_size": page_size, "layers": layers,
             "frac_of_hbm_peak": gbs / pk["hbm"],
             "l2": "four layers' pools, 2.8 GB, cycled: inputs larger than L2"}
+
+
+def split_kv_leg(torch, ops, orc, world, rank, dev, barrier, pk, layers=16, reps=20):
+    """cfg5 decode: one sequence of 32768 cached positions, bf16 GQA 40/8, the cache sharded by
+    POSITION over the ranks; every rank attends over its slice, the (O, LSE) partials are exchanged
+    and merged (all ranks get the output).  Timed per layer for both exchanges: NCCL all-gather +
+    merge kernel, and the one-kernel exchange over peer memory.  `layers` layers with caches of
+    their own are cycled so that a rank's working set exceeds L2 at 8 GPUs (16 x 16.8 MB)."""
+    import torch.distributed as dist
+    from llm_simple_b200 import sharding
+    c = CFG5
+    H, kvh, L = c["n_heads"], c["n_kv_heads"], c["seq"]
+    lo, hi = sharding.position_slices(L, world)[rank]
+    n_loc = hi - lo
+    cap = n_loc + 136
+    tail = rank == world - 1
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(20255 + rank)
+    kc = [torch.empty((1, kvh, cap, D), dtype=torch.bfloat16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    vc = [torch.empty((1, kvh, cap, D), dtype=torch.bfloat16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    q = torch.empty((layers, 1, H * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    k = torch.empty((layers, 1, kvh * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    v = torch.empty((layers, 1, kvh * D), dtype=torch.bfloat16, device=dev).normal_(generator=gen)
+    out = torch.empty((layers, 1, H * D), dtype=torch.bfloat16, device=dev)
+    table = torch.from_numpy(orc.init_freq_cis(D, L + 8, c["theta"], orc.DT_BFLOAT16)).to(dev)
+    desc = ops.make_desc(DT_BF16, 1, H, kvh, 1, cap, layout="head", is_neox=c["neox"])
+    desc.total_kv_len = n_loc + 1
+    ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, cap)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    len_d = torch.tensor([n_loc], dtype=torch.int32, device=dev)
+    pos_d = torch.tensor([L], dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream()
+    nbytes = decode_bytes([L + 1], H, kvh)
+    res = {"workload": "cfg5 decode step, 32768 cached positions, position-sharded x%d" % world,
+           "bytes_per_layer": nbytes, "layers_cycled": layers}
+
+    def timed(step):
+        for _ in range(3):
+            step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        us = ms * 1e3 / (reps * layers)
+        return {"us_per_layer": us, "gbs": nbytes / (us * 1e-6) / 1e9}
+
+    if world == 1:
+        def step():
+            for l in range(layers):
+                ops.gpu_attn_decode_layer(desc, out[l], None, None, q[l], k[l], v[l], kc[l], vc[l], table, len_d, pos_d,
+                                          True, n_loc + 1, ws, ws_bytes, stream=stream)
+        res["single_gpu"] = timed(step)
+        return res
+    for mode in ("nccl", "peer"):
+        dec = sharding.SplitKVDecoder(desc, DT_BF16, exchange=mode)
+
+        def step():
+            for l in range(layers):
+                dec.step(out[l], q[l], k[l], v[l], kc[l], vc[l], table, len_d, pos_d, n_loc, ws, ws_bytes)
+        res[mode] = timed(step)
+        dec.close()
+    res["kernel_status"] = ops.gpu_ops_kernel_status()
+    return res
 
 
 def long_prefill_leg(torch, ops, orc, world, dev, barrier, pk, flush):
