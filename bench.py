@@ -236,6 +236,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip prefill leg, e2e and CPU baseline")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="on ONE GPU, run rank 0's shard of an N-way KV-head split (sizing a multi-GPU shard)")
+    ap.add_argument("--early-prefetch", type=int, default=1,
+                    help="1: the decode kernel requests its first K/V tiles before the preceding kernels of the "
+                         "stream have finished (legal here: consecutive launches read different layers' caches)")
     ap.add_argument("--graph", type=int, default=1,
                     help="1: replay the step's launches from a CUDA graph (default), 0: launch them one by one")
     ap.add_argument("--leg", default="all", choices=["all", "prefill"],
@@ -315,6 +318,9 @@ def main():
     ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, max_kv)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()
+
+    # consecutive launches work on different layers' caches and the lengths are fixed for the step
+    ops.gpu_attn_set_decode_early_prefetch(args.early_prefetch)
 
     def step():
         for l in range(layers):
@@ -415,6 +421,7 @@ def main():
                                "rank 0's shard of a kv-head x%d split, alone on one GPU" % split,
                    "launch": "cuda graph of the step's %d launches" % launches_per_step if graph is not None
                              else "one call per layer",
+                   "early_kv_prefetch": bool(args.early_prefetch),
                    "cache_layout": "head-major",
                    "l2": "inputs larger than L2 (%.0f MB per layer, %.1f GB per step per rank)"
                          % (bytes_layer_rank / 1e6, bytes_layer_rank * layers / 1e9)},

@@ -332,6 +332,16 @@ int gpu_attn_merge_packed_layer(void *out, const float *parts, int n_parts, int 
  * Calls that share the scratch must be ordered on one stream. */
 int gpu_ops_set_workspace(void *workspace, size_t bytes);
 
+/* 1: gpu_attn_decode_layer (flat or paged) requests its first K/V tiles BEFORE
+ * the kernels that precede it on the stream have finished, which hides its
+ * start-up latency behind their tail.  Allowed when neither kv_len_dev nor the
+ * cache rows below kv_len[b] of a call are written by the TWO kernels preceding
+ * it on the stream -- the case when consecutive calls work on different layers'
+ * caches and the lengths change once per step.  Everything else the call reads
+ * (q, the new token, the scratch) is still ordered after those kernels.
+ * Process-wide, off by default. */
+int gpu_attn_set_decode_early_prefetch(int on);
+
 /* Positions per split used by gpu_attn_decode_layer; 0 restores the built-in
  * choice.  A multiple of 64.  Process-wide tuning knob. */
 int gpu_attn_set_decode_chunk(int positions);

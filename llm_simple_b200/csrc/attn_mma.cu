@@ -45,8 +45,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
   // Launched with programmatic stream serialisation: this grid may be scheduled while
   // the previous kernel of the stream is still draining.  Let the next one in as early
   // as possible, and touch no memory before the previous grid has completed and flushed.
+  // With early_kv the caller guarantees that the length array and the cached rows below
+  // kv_len are older than the two kernels that precede this one on the stream (consecutive
+  // calls work on different layers' caches), so the first K/V tiles are requested before the
+  // wait and the start-up latency of this kernel overlaps the tail of the previous ones.
   cudaTriggerProgrammaticLaunchCompletion();
-  cudaGridDependencySynchronize();
+  if (!p.early_kv) cudaGridDependencySynchronize();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.g.group;
@@ -100,6 +104,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
     if (s < ntiles) load_tile(s);
     cp_async_commit();
   }
+
+  if (p.early_kv) cudaGridDependencySynchronize();
 
   // ---- query rows -> shared memory (rotated here when the caller passes raw q)
   const int rope_row = (p.rope_pos_dev ? p.rope_pos_dev[b] : len_old);

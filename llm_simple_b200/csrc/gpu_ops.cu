@@ -21,6 +21,7 @@ thread_local std::string g_last_error;
 thread_local long g_launches = 0;
 std::atomic<int> g_decode_chunk{0};
 std::atomic<int> g_prefill_kernel{0};
+std::atomic<int> g_decode_early{0};
 
 // caller-registered scratch for the reference-shaped operators, per device
 struct RegisteredWorkspace {
@@ -581,6 +582,7 @@ static int decode_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, v
   p.is_neox = desc->is_neox_style ? 1 : 0;
   p.scale_log2 = scale_log2_of(desc->head_dim);
   p.pg = pg;
+  p.early_kv = g_decode_early.load();
   p.chunk = pick_chunk(desc->batch, desc->n_kv_heads, desc->total_kv_len, max_kv_len);
   p.max_splits = (max_kv_len + p.chunk - 1) / p.chunk;
   if (p.max_splits > 1) {
@@ -762,6 +764,11 @@ int gpu_ops_set_workspace(void *workspace, size_t bytes) {
 int gpu_attn_set_decode_chunk(int positions) {
   if (positions < 0 || positions % 64) return fail(GPU_OPS_E_INVALID, "chunk %d: a non-negative multiple of 64", positions);
   g_decode_chunk.store(positions);
+  return GPU_OPS_OK;
+}
+
+int gpu_attn_set_decode_early_prefetch(int on) {
+  g_decode_early.store(on ? 1 : 0);
   return GPU_OPS_OK;
 }
 

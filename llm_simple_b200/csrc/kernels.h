@@ -85,6 +85,7 @@ struct DecodeParams {
   float *ws_lse;        // [rows][max_splits] (log2 domain)
   float scale_log2;
   KvPaging pg;
+  int early_kv;         // 1: fetch the first K/V tiles before waiting for the preceding kernels
 };
 
 cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t stream, int *launches);

@@ -25,7 +25,7 @@ EXPORTS = [
     "gpu_attn_decode_paged_layer", "gpu_attn_prefill_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_attn_xchg_buffer_bytes", "gpu_attn_xchg_local_slot", "gpu_attn_xchg_merge_layer",
     "gpu_peer_buffer_alloc", "gpu_peer_buffer_open", "gpu_peer_buffer_close", "gpu_peer_buffer_free",
-    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_prefill_kernel",
+    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
 ]
 
@@ -131,6 +131,7 @@ def lib():
         L.gpu_peer_buffer_free.argtypes = [vp]
         L.gpu_ops_set_workspace.argtypes = [vp, ctypes.c_size_t]
         L.gpu_attn_set_decode_chunk.argtypes = [i]
+        L.gpu_attn_set_decode_early_prefetch.argtypes = [i]
         L.gpu_attn_set_prefill_kernel.argtypes = [i]
         L.gpu_ops_launch_count.argtypes = [i]
         L.gpu_ops_launch_count.restype = ctypes.c_long
@@ -313,6 +314,10 @@ def gpu_attn_merge_packed_layer(out, parts, n_parts, rows, head_dim, dt, stream=
 
 def gpu_ops_set_workspace(workspace, nbytes):
     _check(lib().gpu_ops_set_workspace(_ptr(workspace), nbytes))
+
+
+def gpu_attn_set_decode_early_prefetch(on):
+    _check(lib().gpu_attn_set_decode_early_prefetch(int(bool(on))))
 
 
 def gpu_attn_set_decode_chunk(positions):

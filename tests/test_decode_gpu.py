@@ -224,3 +224,42 @@ def test_decode_rejects_missing_workspace_and_bad_arguments(ops):
     desc.n_kv_heads = 40
     with pytest.raises(ops.GpuOpsError):
         ops.gpu_attn_decode_layer(desc, x, None, None, x, x, x, x, x, tab, lens, None, True, 64, None, 0)
+
+
+def test_early_prefetch_gives_the_same_bits(ops):
+    """Four layers with caches of their own, three steps: with the early K/V prefetch on, every output
+    and every appended row equals the default ordering bit for bit (the usage the option is meant for:
+    consecutive launches never read a cache the preceding kernels write)."""
+    dt, H, kvh, batch, max_pos, layers = BF16, 10, 2, 6, 700, 4
+    lens0 = np.array([600, 1, 64, 255, 0, 333], dtype=np.int32)
+    table = torch.from_numpy(orc.init_freq_cis(D, max_pos, 1e6, dt)).cuda()
+    desc = ops.make_desc(dt, batch, H, kvh, 1, max_pos, layout="head", is_neox=True)
+    ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, max_pos)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    results = []
+    for early in (0, 1):
+        ops.gpu_attn_set_decode_early_prefetch(early)
+        try:
+            kc = [dev(rnd_bits((batch, kvh, max_pos, D), dt, 500 + l), dt) for l in range(layers)]
+            vc = [dev(rnd_bits((batch, kvh, max_pos, D), dt, 600 + l), dt) for l in range(layers)]
+            lens = torch.from_numpy(lens0.copy()).cuda()
+            outs = []
+            for step in range(3):
+                for l in range(layers):
+                    q = dev(rnd_bits((batch, H * D), dt, 1000 + 10 * step + l), dt)
+                    k = dev(rnd_bits((batch, kvh * D), dt, 2000 + 10 * step + l), dt)
+                    v = dev(rnd_bits((batch, kvh * D), dt, 3000 + 10 * step + l), dt)
+                    o = torch.empty((batch, H * D), dtype=torch.bfloat16, device="cuda")
+                    ops.gpu_attn_decode_layer(desc, o, None, None, q, k, v, kc[l], vc[l], table, lens, None, True,
+                                              int(lens0.max()) + step + 1, ws, ws_bytes)
+                    outs.append(o)
+                torch.cuda.synchronize()      # the lengths change between steps, not between layers
+                lens += 1
+            results.append((outs, kc, vc))
+        finally:
+            ops.gpu_attn_set_decode_early_prefetch(0)
+    for a, b in zip(results[0][0], results[1][0]):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    for l in range(layers):
+        assert torch.equal(results[0][1][l].view(torch.int16), results[1][1][l].view(torch.int16))
+        assert torch.equal(results[0][2][l].view(torch.int16), results[1][2][l].view(torch.int16))
