@@ -59,7 +59,7 @@ constexpr float kRescaleThreshold = 8.0f;        // log2 domain
 
 // barrier slots (8 bytes each) inside the barrier block; X = 0 (tile A) or 1 (tile B)
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_PHALF = 15, BAR_COUNT = 17 };
+       BAR_ODONE = 13, BAR_PHALF = 15, BAR_QB = 17, BAR_COUNT = 18 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -243,6 +243,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   auto bar = [&](int i) { return bar_base + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
   const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / p.group;
   const int row0 = qb * 2 * kBM;                 // first row of tile A; tile B starts kBM later
@@ -254,8 +259,43 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t idesc_qk = instr_desc(fmt, 0), idesc_pv = instr_desc(fmt, 1);
 
+  // K / V tile j of this CTA's KV head: coordinates (flat or paged) and the map to read it through.
+  // Flat cache: (d, position, kv head, sequence); rows at and beyond n are outside the map and read
+  // as zero.  Paged cache: (d, position in page, kv head, page); the page that holds position n - 1
+  // is read through a second map that ends at that position, so that the unwritten rest of the page
+  // reads as zero too.
+  auto load_kv_tile = [&](int j, bool is_k) {
+    const int s = j % kStages;
+    int c1 = j * kBN, c3 = b;
+    const CUtensorMap *mp = is_k ? &map_k : &map_v;
+    if (p.page_table) {
+      const int pi = c1 >> p.page_shift;
+      c3 = p.page_table[static_cast<long>(b) * p.table_stride + pi];
+      c1 &= (1 << p.page_shift) - 1;
+      if (pi == ((p.n - 1) >> p.page_shift)) mp = is_k ? &map_k_tail : &map_v_tail;
+    }
+    const uint32_t full = bar((is_k ? BAR_KFULL : BAR_VFULL) + s);
+    const uint32_t dst = smem_base + (is_k ? kSmemK : kSmemV) + s * kTileBytes;
+    mbar_expect_tx(full, kTileBytes);
+    tma_load_4d(dst, mp, full, 0, c1, kvh, c3);
+    tma_load_4d(dst + kHalfTile, mp, full, 64, c1, kvh, c3);
+  };
+  auto load_q_tile = [&](int x) {
+    const uint32_t qbar = bar(x ? BAR_QB : BAR_Q);
+    mbar_expect_tx(qbar, kTileBytes);
+    tma_load_4d(smem_base + kSmemQ + x * kTileBytes, &map_q, qbar, 0, h, row0 + x * kBM, b);
+    tma_load_4d(smem_base + kSmemQ + x * kTileBytes + kHalfTile, &map_q, qbar, 64, h, row0 + x * kBM, b);
+  };
+  auto issue_first_loads = [&]() {
+    load_q_tile(0);
+    if (nt > 0) load_kv_tile(0, true);
+    if (nt > 0) load_kv_tile(0, false);
+    if (has_b) load_q_tile(1);
+  };
+
   if (threadIdx.x == 0) {
     mbar_init(bar(BAR_Q), 1);
+    mbar_init(bar(BAR_QB), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_KFULL + s), 1);
       mbar_init(bar(BAR_KEMPTY + s), 1);
@@ -268,6 +308,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The first loads leave before TMEM is allocated and the other warps are released, so
+    // that their latency (about 2500 cycles from a cold start) overlaps the set-up: Q_A and
+    // the first K tile (what the first MMAs need), then the first V tile, then Q_B.
+    issue_first_loads();
   }
   if (warp == 0) {
     __syncwarp();
@@ -286,37 +330,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     reg_dec<64>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer
-      mbar_expect_tx(bar(BAR_Q), has_b ? 2 * kTileBytes : kTileBytes);
-      for (int x = 0; x < (has_b ? 2 : 1); ++x) {
-        tma_load_4d(smem_base + kSmemQ + x * kTileBytes, &map_q, bar(BAR_Q), 0, h, row0 + x * kBM, b);
-        tma_load_4d(smem_base + kSmemQ + x * kTileBytes + kHalfTile, &map_q, bar(BAR_Q), 64, h, row0 + x * kBM, b);
-      }
-      for (int j = 0; j < nt; ++j) {
+      for (int j = 1; j < nt; ++j) {   // tile 0 left before the set-up barrier
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
-        // Flat cache: coordinates (d, position, kv head, sequence); rows at and beyond n are
-        // outside the map and read as zero.  Paged cache: (d, position in page, kv head, page);
-        // the page that holds position n - 1 is read through a second map that ends at that
-        // position, so that the unwritten rest of the page reads as zero too.
-        int c1 = j * kBN, c3 = b;
-        const CUtensorMap *mk = &map_k, *mv = &map_v;
-        if (p.page_table) {
-          const int pi = c1 >> p.page_shift;
-          c3 = p.page_table[static_cast<long>(b) * p.table_stride + pi];
-          c1 &= (1 << p.page_shift) - 1;
-          if (pi == ((p.n - 1) >> p.page_shift)) {
-            mk = &map_k_tail;
-            mv = &map_v_tail;
-          }
-        }
         if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) break;
-        mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
-        tma_load_4d(smem_base + kSmemK + s * kTileBytes, mk, bar(BAR_KFULL + s), 0, c1, kvh, c3);
-        tma_load_4d(smem_base + kSmemK + s * kTileBytes + kHalfTile, mk, bar(BAR_KFULL + s), 64, c1, kvh, c3);
+        load_kv_tile(j, true);
         if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2)) break;
-        mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
-        tma_load_4d(smem_base + kSmemV + s * kTileBytes, mv, bar(BAR_VFULL + s), 0, c1, kvh, c3);
-        tma_load_4d(smem_base + kSmemV + s * kTileBytes + kHalfTile, mv, bar(BAR_VFULL + s), 64, c1, kvh, c3);
+        load_kv_tile(j, false);
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------- MMA issuer
@@ -371,7 +391,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       };
       // tile B (when present) reads every KV tile that A reads, and reads it after A
       if (ok && nt_a > 0) ok = issue_qk(0, 0, !has_b);
-      if (ok && has_b) ok = issue_qk(1, 0, true);
+      if (ok && has_b) {
+        ok = mbar_wait(bar(BAR_QB), 0, abort_flag, p.error_flag, 11);
+        if (ok) ok = issue_qk(1, 0, true);
+      }
       for (int j = 0; ok && j < nt; ++j) {
         if (j < nt_a) {
           ok = issue_pv(0, j, !has_b);
