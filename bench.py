@@ -434,6 +434,7 @@ def main():
         line["prefill"] = prefill_leg(torch, ops, orc, world, dev, barrier, pk)
         line["cfg5_split_kv_decode"] = split_kv_leg(torch, ops, orc, world, rank, dev, barrier, pk)
         if world == 1:
+            line["other_configs"] = other_configs_leg(torch, ops, orc, dev, pk)
             line["paged_decode"] = paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, kvh_l, dev,
                                              pk)
         if rank == 0 and world == 1:
@@ -558,6 +559,93 @@ def paged_leg(torch, ops, cfg, lens, lens_d, table, ws, ws_bytes, max_kv, H_l, k
     return {"value": gbs, "unit": "GB/s", "ms_per_layer": ms_layer, "page_size": page_size, "layers": layers,
             "frac_of_hbm_peak": gbs / pk["hbm"],
             "l2": "four layers' pools, 2.8 GB, cycled: inputs larger than L2"}
+
+
+def other_configs_leg(torch, ops, orc, dev, pk):
+    """The remaining configurations on one GPU, one figure each: cfg1 (Llama-2-7B-shaped prefill,
+    m = n = 256: launch-bound), cfg2 (Qwen2.5-1.5B-shaped one-sequence decode step: latency-bound,
+    28 layers replayed from a graph), cfg3's decode phase (batch 8, MHA 40 heads, about 2176 cached
+    positions: HBM-bound with one query row per KV head)."""
+    stream = torch.cuda.current_stream()
+    res = {}
+
+    def time_us(fn, reps, inner=1):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * inner)
+
+    # ---- cfg1
+    m, H = 256, 32
+    q = torch.randn((m, H * D), dtype=torch.float16, device=dev)
+    k, v, o = torch.randn_like(q), torch.randn_like(q), torch.empty_like(q)
+    us = time_us(lambda: ops.gpu_flash_attn_layer(o, q, k, v, m, m, 0, H, D, DT_FP16, stream=stream), 200)
+    fl = prefill_flops(1, H, m, 0)
+    res["cfg1_prefill"] = {"us": us, "tflops": fl / (us * 1e-6) / 1e12, "note": "m = n = 256, 32 heads, fp16; launch-bound "
+                           "(0.54 GFLOP), inputs stay in L2"}
+    # ---- cfg2
+    layers, Hq, kvh, L, max_pos = 28, 12, 2, 640, 776
+    kc = [torch.randn((1, kvh, max_pos, D), dtype=torch.bfloat16, device=dev) for _ in range(layers)]
+    vc = [torch.randn((1, kvh, max_pos, D), dtype=torch.bfloat16, device=dev) for _ in range(layers)]
+    q2 = torch.randn((layers, 1, Hq * D), dtype=torch.bfloat16, device=dev)
+    k2 = torch.randn((layers, 1, kvh * D), dtype=torch.bfloat16, device=dev)
+    v2 = torch.randn_like(k2)
+    o2 = torch.empty_like(q2)
+    table = torch.from_numpy(orc.init_freq_cis(D, max_pos, 1e6, orc.DT_BFLOAT16)).to(dev)
+    desc = ops.make_desc(DT_BF16, 1, Hq, kvh, 1, max_pos, layout="head", is_neox=True)
+    desc.total_kv_len = L + 1
+    wsb = ops.gpu_attn_decode_workspace_bytes(desc, L + 1)
+    ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+    len_d = torch.tensor([L], dtype=torch.int32, device=dev)
+
+    def step2(st):
+        for l in range(layers):
+            ops.gpu_attn_decode_layer(desc, o2[l], None, None, q2[l], k2[l], v2[l], kc[l], vc[l], table, len_d, None, True,
+                                      L + 1, ws, wsb, stream=st)
+    step2(stream)
+    torch.cuda.synchronize()
+    cap = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(cap):
+        graph.capture_begin()
+        step2(cap)
+        graph.capture_end()
+    us_call = time_us(lambda: step2(stream), 20, layers)
+    us_graph = time_us(graph.replay, 50, layers)
+    res["cfg2_decode"] = {"us_per_layer_graph": us_graph, "us_per_layer_calls": us_call,
+                          "bytes_per_layer": decode_bytes([L + 1], Hq, kvh),
+                          "note": "batch 1, 12/2 heads, 640 cached positions (0.66 MB per layer): latency-bound; the "
+                                  "28 layers' caches (18 MB) stay in L2"}
+    # ---- cfg3 decode phase
+    B, H3, L3, max3 = 8, 40, 2176, 2304
+    nl = 4
+    kc3 = [torch.randn((B, H3, max3, D), dtype=torch.float16, device=dev) for _ in range(nl)]
+    vc3 = [torch.randn((B, H3, max3, D), dtype=torch.float16, device=dev) for _ in range(nl)]
+    q3 = torch.randn((nl, B, H3 * D), dtype=torch.float16, device=dev)
+    k3, v3, o3 = torch.randn_like(q3), torch.randn_like(q3), torch.empty_like(q3)
+    t3 = torch.from_numpy(orc.init_freq_cis(D, max3, 1e4, orc.DT_FLOAT16)).to(dev)
+    d3 = ops.make_desc(DT_FP16, B, H3, H3, 1, max3, layout="head", is_neox=False)
+    d3.total_kv_len = B * (L3 + 1)
+    wsb3 = ops.gpu_attn_decode_workspace_bytes(d3, L3 + 1)
+    ws3 = torch.empty(max(wsb3, 16), dtype=torch.uint8, device=dev)
+    len3 = torch.full((B,), L3, dtype=torch.int32, device=dev)
+
+    def step3():
+        for l in range(nl):
+            ops.gpu_attn_decode_layer(d3, o3[l], None, None, q3[l], k3[l], v3[l], kc3[l], vc3[l], t3, len3, None, True,
+                                      L3 + 1, ws3, wsb3, stream=stream)
+    us3 = time_us(step3, 20, nl)
+    nb3 = decode_bytes([L3 + 1] * B, H3, H3)
+    gbs3 = nb3 / (us3 * 1e-6) / 1e9
+    res["cfg3_decode"] = {"us_per_layer": us3, "gbs": gbs3, "frac_of_hbm_peak": gbs3 / pk["hbm"], "bytes_per_layer": nb3,
+                          "note": "batch 8, 40 heads MHA, 2176 cached positions, fp16; four layers' caches (2.9 GB) cycled"}
+    return res
 
 
 def split_kv_leg(torch, ops, orc, world, rank, dev, barrier, pk, layers=16, reps=20):

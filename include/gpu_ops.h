@@ -254,6 +254,19 @@ int gpu_attn_xchg_merge_layer(void *out, void *local_buffer, void *const *peer_b
                               int rank, uint32_t epoch, int rows, int head_dim, int dt,
                               gpu_stream_t stream);
 
+/* gpu_attn_decode_layer and gpu_attn_xchg_merge_layer as one call of two launches:
+ * the decode kernel leaves this rank's partial split along the cache in the
+ * workspace, and the exchange kernel merges a row's splits, pushes the row to
+ * the peers and merges the ranks' rows -- one launch less than decode + local
+ * merge + exchange, same bits.  Arguments as for the two functions. */
+int gpu_attn_decode_xchg_layer(const gpu_attn_desc *desc, void *out, const void *q_in,
+                               const void *k_in, const void *v_in, void *k_cache, void *v_cache,
+                               const void *freqs_cis_dev, const int32_t *kv_len_dev,
+                               const int32_t *rope_pos_dev, int append_new, int max_kv_len,
+                               void *workspace, size_t workspace_bytes, void *local_buffer,
+                               void *const *peer_buffers, int world, int rank, uint32_t epoch,
+                               gpu_stream_t stream);
+
 /* Device memory that other processes of the node can map: cudaMalloc + zero
  * fill + IPC export (handle64: 64 bytes to hand to the peers), import, unmap,
  * free.  Allocation helpers, not operators: call them at start-up. */

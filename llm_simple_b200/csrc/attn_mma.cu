@@ -440,7 +440,7 @@ cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t st
   if (e != cudaSuccess) return e;
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   *launches = 1;
-  if (p.max_splits > 1) {
+  if (p.max_splits > 1 && !p.no_merge) {
     MergeParams mp{};
     mp.out = p.out;
     mp.o_partial = p.o_partial;

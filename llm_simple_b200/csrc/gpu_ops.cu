@@ -541,12 +541,87 @@ size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len
   return decode_ws_bytes(static_cast<long>(desc->batch) * desc->n_heads, splits);
 }
 
+// ---- cross-device exchange over peer memory ----------------------------------
+namespace {
+size_t align16(size_t x) { return (x + 15) & ~static_cast<size_t>(15); }
+size_t xchg_slots_bytes(int world, int rows) { return align16(static_cast<size_t>(world) * rows * 129 * 4); }
+size_t xchg_half_bytes(int world, int rows) {
+  return xchg_slots_bytes(world, rows) + align16(static_cast<size_t>(world) * rows * 4);
+}
+
+struct XchgRequest {
+  void *local;
+  void *const *peers;
+  int world, rank;
+  uint32_t epoch;
+};
+
+// Addresses of one step's buffer half on this rank and on its peers.
+int build_xchg(XchgParams *p, const XchgRequest &x, int rows) {
+  if (!x.local || !x.peers) return fail(GPU_OPS_E_INVALID, "null pointer");
+  if (x.world < 1 || x.world > kMaxPeers || x.rank < 0 || x.rank >= x.world || rows <= 0 || x.epoch == 0)
+    return fail(GPU_OPS_E_INVALID, "world %d (1..%d), rank %d, rows %d, epoch %u", x.world, kMaxPeers, x.rank, rows,
+                x.epoch);
+  *p = XchgParams{};
+  const size_t half = (x.epoch & 1u) * xchg_half_bytes(x.world, rows);
+  const size_t n = static_cast<size_t>(rows) * 129;
+  char *lb = static_cast<char *>(x.local) + half;
+  p->slots = reinterpret_cast<const float *>(lb);
+  p->flags = reinterpret_cast<const uint32_t *>(lb + xchg_slots_bytes(x.world, rows));
+  for (int r = 0; r < x.world; ++r) {
+    if (r == x.rank) continue;
+    if (!x.peers[r]) return fail(GPU_OPS_E_INVALID, "peer buffer %d is null", r);
+    char *pb = static_cast<char *>(x.peers[r]) + half;
+    p->peer_slot[r] = reinterpret_cast<float *>(pb) + static_cast<size_t>(x.rank) * n;
+    p->peer_flag[r] = reinterpret_cast<uint32_t *>(pb + xchg_slots_bytes(x.world, rows)) + static_cast<size_t>(x.rank) * rows;
+  }
+  p->epoch = x.epoch;
+  p->world = x.world;
+  p->rank = x.rank;
+  p->rows = rows;
+  p->error_flag = kernel_error_word_dev();
+  if (!p->error_flag) return fail(GPU_OPS_E_CUDA, "no status word");
+  return GPU_OPS_OK;
+}
+} // namespace
+
+size_t gpu_attn_xchg_buffer_bytes(int world, int rows) {
+  if (world <= 0 || rows <= 0) return 0;
+  return 2 * xchg_half_bytes(world, rows);
+}
+
+float *gpu_attn_xchg_local_slot(void *local_buffer, int world, int rank, uint32_t epoch, int rows) {
+  if (!local_buffer || world <= 0 || rank < 0 || rank >= world || rows <= 0) return nullptr;
+  char *half = static_cast<char *>(local_buffer) + (epoch & 1u) * xchg_half_bytes(world, rows);
+  return reinterpret_cast<float *>(half) + static_cast<size_t>(rank) * rows * 129;
+}
+
+int gpu_attn_xchg_merge_layer(void *out, void *local_buffer, void *const *peer_buffers, int world, int rank,
+                              uint32_t epoch, int rows, int head_dim, int dt, gpu_stream_t stream) {
+  if (int rc = check_common(dt, head_dim)) return rc;
+  if (!out) return fail(GPU_OPS_E_INVALID, "null pointer");
+  XchgParams p;
+  if (int rc = build_xchg(&p, XchgRequest{local_buffer, peer_buffers, world, rank, epoch}, rows)) return rc;
+  p.out = out;
+  cudaError_t e = launch_attn_xchg_merge(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "exchange + merge launch");
+  g_launches += 1;
+  return GPU_OPS_OK;
+}
+
 static int decode_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, void *out, float *o_partial,
                          float *lse_partial, const void *q_in, const void *k_in, const void *v_in, void *k_cache,
                          void *v_cache, const void *freqs_cis_dev, const int32_t *kv_len_dev,
                          const int32_t *rope_pos_dev, int append_new, int max_kv_len, void *workspace,
-                         size_t workspace_bytes, gpu_stream_t stream) {
+                         size_t workspace_bytes, gpu_stream_t stream, const XchgRequest *xchg = nullptr) {
   if (int rc = check_desc(desc)) return rc;
+  XchgParams xp;
+  if (xchg) {
+    // the partial goes to this rank's slot of the exchange buffer, or stays split for the exchange kernel
+    if (int rc = build_xchg(&xp, *xchg, desc->batch * desc->n_heads)) return rc;
+    o_partial = gpu_attn_xchg_local_slot(xchg->local, xchg->world, xchg->rank, xchg->epoch, desc->batch * desc->n_heads);
+    lse_partial = o_partial + static_cast<size_t>(desc->batch) * desc->n_heads * 128;
+  }
   KvPaging pg;
   if (int rc = paging_from(pages, &pg)) return rc;
   const int group = desc->n_heads / desc->n_kv_heads;
@@ -593,11 +668,38 @@ static int decode_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, v
     p.ws_o = static_cast<float *>(workspace);
     p.ws_lse = p.ws_o + rows * p.max_splits * 128;
   }
+  if (xchg) p.no_merge = 1;
   int launches = 0;
   cudaError_t e = launch_attn_decode(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream), &launches);
   g_launches += launches;
   if (e != cudaSuccess) return cuda_fail(e, "decode attention launch");
+  if (xchg) {
+    xp.out = out;
+    if (p.max_splits > 1) {
+      xp.ws_o = p.ws_o;
+      xp.ws_lse = p.ws_lse;
+      xp.max_splits = p.max_splits;
+      xp.chunk = p.chunk;
+      xp.append = p.append;
+      xp.rows_per_seq = desc->n_heads;
+      xp.kv_len_dev = kv_len_dev;
+    }
+    e = launch_attn_xchg_merge(xp, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "exchange + merge launch");
+    g_launches += 1;
+  }
   return GPU_OPS_OK;
+}
+
+int gpu_attn_decode_xchg_layer(const gpu_attn_desc *desc, void *out, const void *q_in, const void *k_in,
+                               const void *v_in, void *k_cache, void *v_cache, const void *freqs_cis_dev,
+                               const int32_t *kv_len_dev, const int32_t *rope_pos_dev, int append_new, int max_kv_len,
+                               void *workspace, size_t workspace_bytes, void *local_buffer, void *const *peer_buffers,
+                               int world, int rank, uint32_t epoch, gpu_stream_t stream) {
+  if (!out) return fail(GPU_OPS_E_INVALID, "null pointer");
+  const XchgRequest x{local_buffer, peer_buffers, world, rank, epoch};
+  return decode_common(desc, nullptr, out, nullptr, nullptr, q_in, k_in, v_in, k_cache, v_cache, freqs_cis_dev,
+                       kv_len_dev, rope_pos_dev, append_new, max_kv_len, workspace, workspace_bytes, stream, &x);
 }
 
 int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial, float *lse_partial,
@@ -656,56 +758,6 @@ int gpu_attn_merge_packed_layer(void *out, const float *parts, int n_parts, int 
   const long stride = static_cast<long>(rows) * (128 + 1);
   return merge_parts(out, parts, parts + static_cast<long>(rows) * 128, stride, stride, n_parts, rows, head_dim, dt,
                      stream);
-}
-
-// ---- cross-device exchange over peer memory ----------------------------------
-namespace {
-size_t align16(size_t x) { return (x + 15) & ~static_cast<size_t>(15); }
-size_t xchg_slots_bytes(int world, int rows) { return align16(static_cast<size_t>(world) * rows * 129 * 4); }
-size_t xchg_half_bytes(int world, int rows) { return xchg_slots_bytes(world, rows) + align16(static_cast<size_t>(world) * 4); }
-} // namespace
-
-size_t gpu_attn_xchg_buffer_bytes(int world, int rows) {
-  if (world <= 0 || rows <= 0) return 0;
-  return 2 * xchg_half_bytes(world, rows);
-}
-
-float *gpu_attn_xchg_local_slot(void *local_buffer, int world, int rank, uint32_t epoch, int rows) {
-  if (!local_buffer || world <= 0 || rank < 0 || rank >= world || rows <= 0) return nullptr;
-  char *half = static_cast<char *>(local_buffer) + (epoch & 1u) * xchg_half_bytes(world, rows);
-  return reinterpret_cast<float *>(half) + static_cast<size_t>(rank) * rows * 129;
-}
-
-int gpu_attn_xchg_merge_layer(void *out, void *local_buffer, void *const *peer_buffers, int world, int rank,
-                              uint32_t epoch, int rows, int head_dim, int dt, gpu_stream_t stream) {
-  if (int rc = check_common(dt, head_dim)) return rc;
-  if (!out || !local_buffer || !peer_buffers) return fail(GPU_OPS_E_INVALID, "null pointer");
-  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || rows <= 0 || epoch == 0)
-    return fail(GPU_OPS_E_INVALID, "world %d (1..%d), rank %d, rows %d, epoch %u", world, kMaxPeers, rank, rows, epoch);
-  XchgParams p{};
-  const size_t half = (epoch & 1u) * xchg_half_bytes(world, rows);
-  const size_t n = static_cast<size_t>(rows) * 129;
-  char *lb = static_cast<char *>(local_buffer) + half;
-  p.out = out;
-  p.slots = reinterpret_cast<const float *>(lb);
-  p.flags = reinterpret_cast<const uint32_t *>(lb + xchg_slots_bytes(world, rows));
-  for (int r = 0; r < world; ++r) {
-    if (r == rank) continue;
-    if (!peer_buffers[r]) return fail(GPU_OPS_E_INVALID, "peer buffer %d is null", r);
-    char *pb = static_cast<char *>(peer_buffers[r]) + half;
-    p.peer_slot[r] = reinterpret_cast<float *>(pb) + static_cast<size_t>(rank) * n;
-    p.peer_flag[r] = reinterpret_cast<uint32_t *>(pb + xchg_slots_bytes(world, rows)) + rank;
-  }
-  p.epoch = epoch;
-  p.world = world;
-  p.rank = rank;
-  p.rows = rows;
-  p.error_flag = kernel_error_word_dev();
-  if (!p.error_flag) return fail(GPU_OPS_E_CUDA, "no status word");
-  cudaError_t e = launch_attn_xchg_merge(p, dt == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(e, "exchange + merge launch");
-  g_launches += 1;
-  return GPU_OPS_OK;
 }
 
 int gpu_peer_buffer_alloc(size_t bytes, void **ptr, unsigned char *handle64) {

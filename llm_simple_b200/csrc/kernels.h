@@ -86,6 +86,7 @@ struct DecodeParams {
   float scale_log2;
   KvPaging pg;
   int early_kv;         // 1: fetch the first K/V tiles before waiting for the preceding kernels
+  int no_merge;         // 1: leave the split partials in (ws_o, ws_lse); the caller merges them
 };
 
 cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t stream, int *launches);
@@ -145,6 +146,12 @@ struct XchgParams {
   uint32_t epoch;                 // step counter, never 0
   int world, rank, rows;
   int *error_flag;
+  // Optional: this rank's partial is still split along the cache (decode kernel launched with
+  // no_merge): [rows][max_splits][128] fp32 + [rows][max_splits] log2-domain log-sum-exps; the
+  // kernel merges the splits of a row, pushes the row to the peers and goes on to the final merge.
+  const float *ws_o, *ws_lse;
+  int max_splits, chunk, append, rows_per_seq;
+  const int32_t *kv_len_dev;
 };
 cudaError_t launch_attn_xchg_merge(const XchgParams &p, bool bf16, cudaStream_t stream);
 

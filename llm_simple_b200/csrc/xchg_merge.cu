@@ -20,7 +20,7 @@
 //
 // Buffer of one rank (floats / words), two halves used alternately by
 // consecutive steps so that a fast peer cannot overwrite a slot that is still
-// being merged:  half h: slots [world][rows*129] fp32, then flags [world] u32.
+// being merged:  half h: slots [world][rows*129] fp32, then flags [world][rows] u32.
 // There is no counterpart in the reference, which is single-device.
 #include "kernels.h"
 #include "common.cuh"
@@ -40,11 +40,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 
 } // namespace
 
-// grid: (world - 1) push blocks, then `rows` merge blocks; block: 128 threads
+// Flags: one word per (source rank, query row) in each buffer half, so that a row can be pushed
+// and merged as soon as it exists.
+//
+// grid, partial already merged on this rank (ws_o == nullptr): (world - 1) push blocks, then
+// `rows` merge blocks.  grid, partial still split (ws_o != nullptr): `rows` blocks; each merges
+// its row's splits, pushes the row to every peer itself and then waits for the peers' rows.
+// block: 128 threads.
 template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_kernel(XchgParams p) {
   const int tid = threadIdx.x;
   const long n = static_cast<long>(p.rows) * (kHeadDim + 1);
-  if (static_cast<int>(blockIdx.x) < p.world - 1) {
+  const bool fused = p.ws_o != nullptr;
+  const int n_push = fused ? 0 : p.world - 1;
+  if (static_cast<int>(blockIdx.x) < n_push) {
     // ---- push: this rank's slot -> the same slot in one peer's buffer
     const int peer = static_cast<int>(blockIdx.x) < p.rank ? blockIdx.x : blockIdx.x + 1;
     const float *src = p.slots + static_cast<long>(p.rank) * n;
@@ -52,18 +60,48 @@ template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_ker
     for (long i = tid; i < n; i += blockDim.x) dst[i] = src[i];
     __threadfence_system();
     __syncthreads();
-    if (tid == 0) st_release_sys(p.peer_flag[peer], p.epoch);
+    for (int r = tid; r < p.rows; r += blockDim.x) st_release_sys(p.peer_flag[peer] + r, p.epoch);
     return;
   }
-  // ---- merge: wait for every peer's partial of this step, then combine
-  const int row = blockIdx.x - (p.world - 1), d = tid;
+  const int row = blockIdx.x - n_push, d = tid;
+  if (fused) {
+    // ---- this rank's splits of the row -> one partial (the arithmetic of attn_merge_kernel)
+    const int b = row / p.rows_per_seq;
+    const int total = p.kv_len_dev[b] + p.append;
+    const int n_parts = max(1, (total + p.chunk - 1) / p.chunk);
+    float M = -INFINITY;
+    for (int i = 0; i < n_parts; ++i) M = fmaxf(M, p.ws_lse[static_cast<long>(row) * p.max_splits + i]);
+    float W = 0.f, o = 0.f;
+    if (M != -INFINITY) {
+      for (int i = 0; i < n_parts; ++i) {
+        const float w = exp2f(p.ws_lse[static_cast<long>(row) * p.max_splits + i] - M);
+        W += w;
+        o += w * p.ws_o[(static_cast<long>(row) * p.max_splits + i) * kHeadDim + d];
+      }
+    }
+    const float res = (W > 0.f) ? o / W : 0.f;
+    const float lse = (W > 0.f) ? (M + log2f(W)) * 0.6931471805599453f : -INFINITY;
+    const long o_idx = static_cast<long>(row) * kHeadDim + d, l_idx = static_cast<long>(p.rows) * kHeadDim + row;
+    float *mine = const_cast<float *>(p.slots) + static_cast<long>(p.rank) * n;
+    mine[o_idx] = res;
+    if (d == 0) mine[l_idx] = lse;
+    for (int r = 0; r < p.world; ++r) {
+      if (r == p.rank) continue;
+      p.peer_slot[r][o_idx] = res;
+      if (d == 0) p.peer_slot[r][l_idx] = lse;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.world && tid != p.rank) st_release_sys(p.peer_flag[tid] + row, p.epoch);
+  }
+  // ---- wait for every peer's partial of this row and step, then combine
   __shared__ int s_ok;
   if (tid == 0) {
     int ok = 1;
     const long long t0 = clock64();
     for (int r = 0; r < p.world && ok; ++r) {
       if (r == p.rank) continue;
-      while (ld_acquire_sys(p.flags + r) != p.epoch) {
+      while (ld_acquire_sys(p.flags + static_cast<long>(r) * p.rows + row) != p.epoch) {
         if (clock64() - t0 > 2000000000LL) {
           *reinterpret_cast<volatile int *>(p.error_flag) = 20 + r; // gave up waiting for rank r
           ok = 0;
@@ -76,7 +114,7 @@ template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_ker
   }
   __syncthreads();
   if (!s_ok) return; // the output row stays unwritten; the host sees the status word
-  // the slots were written by other GPUs: read them around L1
+  // the slots were written by other GPUs (and, fused, just now by this block): read them around L1
   auto lse_at = [&](int i) { return __ldcg(p.slots + i * n + static_cast<long>(p.rows) * kHeadDim + row); };
   auto o_at = [&](int i) { return __ldcg(p.slots + i * n + static_cast<long>(row) * kHeadDim + d); };
   float M = -INFINITY;
@@ -94,7 +132,7 @@ template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_ker
 }
 
 cudaError_t launch_attn_xchg_merge(const XchgParams &p, bool bf16, cudaStream_t stream) {
-  const unsigned blocks = static_cast<unsigned>(p.world - 1 + p.rows);
+  const unsigned blocks = static_cast<unsigned>((p.ws_o ? 0 : p.world - 1) + p.rows);
   if (bf16)
     attn_xchg_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(p);
   else

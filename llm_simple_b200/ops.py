@@ -24,6 +24,7 @@ EXPORTS = [
     "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_rope_kv_append_paged_layer",
     "gpu_attn_decode_paged_layer", "gpu_attn_prefill_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_attn_xchg_buffer_bytes", "gpu_attn_xchg_local_slot", "gpu_attn_xchg_merge_layer",
+    "gpu_attn_decode_xchg_layer",
     "gpu_peer_buffer_alloc", "gpu_peer_buffer_open", "gpu_peer_buffer_close", "gpu_peer_buffer_free",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
@@ -125,6 +126,8 @@ def lib():
         L.gpu_attn_xchg_local_slot.argtypes = [vp, i, i, ctypes.c_uint32, i]
         L.gpu_attn_xchg_local_slot.restype = vp
         L.gpu_attn_xchg_merge_layer.argtypes = [vp, vp, ctypes.POINTER(vp), i, i, ctypes.c_uint32, i, i, i, vp]
+        L.gpu_attn_decode_xchg_layer.argtypes = [dp] + [vp] * 7 + [i32p, i32p, i, i, vp, ctypes.c_size_t, vp,
+                                                 ctypes.POINTER(vp), i, i, ctypes.c_uint32, vp]
         L.gpu_peer_buffer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
         L.gpu_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
         L.gpu_peer_buffer_close.argtypes = [vp]
@@ -301,6 +304,16 @@ def gpu_attn_xchg_merge_layer(out, local_buffer, peer_buffers, world, rank, epoc
     arr = (ctypes.c_void_p * world)(*[p for p in peer_buffers])
     _check(lib().gpu_attn_xchg_merge_layer(_ptr(out), local_buffer, arr, world, rank, epoch, rows, head_dim, dt,
                                            _stream(stream)))
+
+
+def gpu_attn_decode_xchg_layer(desc, out, q_in, k_in, v_in, k_cache, v_cache, freqs_cis, kv_len_dev, rope_pos_dev,
+                               append_new, max_kv_len, workspace, workspace_bytes, local_buffer, peer_buffers, world,
+                               rank, epoch, stream=None):
+    arr = (ctypes.c_void_p * world)(*[p for p in peer_buffers])
+    _check(lib().gpu_attn_decode_xchg_layer(ctypes.byref(desc), _ptr(out), _ptr(q_in), _ptr(k_in), _ptr(v_in),
+                                            _ptr(k_cache), _ptr(v_cache), _ptr(freqs_cis), _ptr(kv_len_dev),
+                                            _ptr(rope_pos_dev), int(bool(append_new)), max_kv_len, _ptr(workspace),
+                                            workspace_bytes, local_buffer, arr, world, rank, epoch, _stream(stream)))
 
 
 def gpu_attn_merge_lse_layer(out, o_parts, lse_parts, n_parts, rows, head_dim, dt, stream=None):

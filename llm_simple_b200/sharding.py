@@ -182,16 +182,23 @@ class SplitKVDecoder:
              workspace, workspace_bytes):
         from . import ops
         tail = self.rank == self.world - 1
-        o_ptr = self.peer.next_slot() if self.peer else self.send.data_ptr()
+        max_len = max_local_len + (1 if tail else 0)
+        if self.peer:
+            # two launches: the decode kernel, then the kernel that merges this rank's splits, pushes
+            # the rows to the peers, waits for theirs and merges
+            pe = self.peer
+            pe.epoch += 1
+            ops.gpu_attn_decode_xchg_layer(self.desc, out, q_in, k_in if tail else None, v_in if tail else None,
+                                           k_cache, v_cache, freqs_cis, local_len_dev, rope_pos_dev, tail, max_len,
+                                           workspace, workspace_bytes, pe.local, pe.peers, pe.world, pe.rank, pe.epoch)
+            return
+        o_ptr = self.send.data_ptr()
         lse_ptr = o_ptr + self.rows * self.desc.head_dim * 4
         ops.gpu_attn_decode_layer(self.desc, None, o_ptr, lse_ptr, q_in, k_in if tail else None,
                                   v_in if tail else None, k_cache, v_cache, freqs_cis, local_len_dev, rope_pos_dev,
-                                  tail, max_local_len + (1 if tail else 0), workspace, workspace_bytes)
-        if self.peer:
-            self.peer.merge(out, self.desc.head_dim, self.dt)
-        else:
-            self.dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
-            ops.gpu_attn_merge_packed_layer(out, self.recv, self.world, self.rows, self.desc.head_dim, self.dt)
+                                  tail, max_len, workspace, workspace_bytes)
+        self.dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        ops.gpu_attn_merge_packed_layer(out, self.recv, self.world, self.rows, self.desc.head_dim, self.dt)
 
     def close(self):
         if self.peer:

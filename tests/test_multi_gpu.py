@@ -180,8 +180,24 @@ def _flow_rank(rank, world, port, ret):
                       torch.tensor([prompt], dtype=torch.int32, device="cuda"), sl_hi - sl_lo, ws, ws_bytes)
             torch.cuda.synchronize()
             same = same and torch.equal(out2.view(torch.int16), out.view(torch.int16))
-        same = same and ops.gpu_ops_kernel_status() == 0
         dec2.close()
+        # ---- the two-call form: decode into this rank's slot, then the exchange kernel with push blocks
+        pe = sharding.PeerExchange(H)
+        tail = rank == world - 1
+        for _ in range(2):
+            slot = pe.next_slot()
+            ops.gpu_attn_decode_layer(desc_d, None, slot, slot + H * D * 4, dev(q[prompt:], dt),
+                                      dev(k[prompt:], dt) if tail else None, dev(v[prompt:], dt) if tail else None,
+                                      k_dst, v_dst, tab_d, torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
+                                      torch.tensor([prompt], dtype=torch.int32, device="cuda"), tail,
+                                      sl_hi - sl_lo + (1 if tail else 0), ws, ws_bytes)
+            out3 = torch.zeros_like(out)
+            pe.merge(out3, D, dt)
+            torch.cuda.synchronize()
+            same = same and torch.equal(out3.view(torch.int16), out.view(torch.int16))
+        dist.barrier()
+        pe.close()
+        same = same and ops.gpu_ops_kernel_status() == 0
         ret[rank] = (host(k_dst[0, :, :sl_hi - sl_lo]), host(v_dst[0, :, :sl_hi - sl_lo]), host(out), host(out_p), same)
     finally:
         dist.destroy_process_group()
