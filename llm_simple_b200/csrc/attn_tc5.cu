@@ -7,7 +7,8 @@
 // sequence, walking the KV cache in tiles of 128 positions up to the causal
 // diagonal.  Twelve warps in three groups of four:
 //   warp 0        TMA producer (one elected lane): Q tiles once, then K and V
-//                 tiles into two-stage rings
+//                 tiles into two-stage rings; the loads of Q and of the first
+//                 K / V tile leave before the set-up barrier of the CTA
 //   warp 1        MMA issuer (one elected lane): S_X = Q_X.K^T (operands from
 //                 shared memory) into TMEM, then O_X += P_X.V with P_X read from
 //                 TMEM and V from shared memory (N-major operand); per KV tile
