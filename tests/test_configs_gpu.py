@@ -147,3 +147,74 @@ def test_cfg5_chunked_prefill_4096_chunks_and_long_decode(ops):
     gold = orc.attn(q_last, k_all, vh, 1, n + 1, n, g, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
     for r in res:
         assert_parity(r, gold[0], dt, "long decode")
+
+
+def test_cfg4_qwen14b_batched_ragged_decode_full_size(ops):
+    """The headline configuration at full size: batch 64, 40 query / 8 KV heads, bf16, cache lengths
+    uniform in [1024, 4096] from the benchmark's seed.  The oracle checks a sample of sequences (shortest,
+    longest, two in between) over all heads; identities cover the rest: the result does not depend on the
+    split size (automatic choice vs forced 512 and 4160 = unsplit) beyond the parity tolerance, a KV-head
+    shard of the call gives the same rows, and the appended rows are the oracle's bits."""
+    dt, H, kvh, batch, neox, theta = BF16, 40, 8, 64, True, 1e6
+    rng = np.random.default_rng(20254)
+    lens = rng.integers(1024, 4097, size=batch).astype(np.int32)
+    max_pos = 4104
+    table_np = orc.init_freq_cis(D, max_pos, theta, dt)
+    table = torch.from_numpy(table_np).cuda()
+    kc0 = randn_bits((batch, kvh, max_pos, D), dt, 1)
+    vc0 = randn_bits((batch, kvh, max_pos, D), dt, 2)
+    q, k, v = randn_bits((batch, H * D), dt, 3), randn_bits((batch, kvh * D), dt, 4), randn_bits((batch, kvh * D), dt, 5)
+    lens_d = torch.from_numpy(lens).cuda()
+    desc = ops.make_desc(dt, batch, H, kvh, 1, max_pos, layout="head", is_neox=neox)
+    desc.total_kv_len = int(lens.sum()) + batch
+    mx = int(lens.max()) + 1
+
+    def run(chunk):
+        ops.gpu_attn_set_decode_chunk(chunk)
+        try:
+            kc, vc = kc0.clone(), vc0.clone()
+            ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, mx)
+            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+            out = torch.empty((batch, H * D), dtype=torch.bfloat16, device="cuda")
+            ops.gpu_attn_decode_layer(desc, out, None, None, q, k, v, kc, vc, table, lens_d, None, True, mx, ws, ws_bytes)
+            torch.cuda.synchronize()
+            return out, kc, vc
+        finally:
+            ops.gpu_attn_set_decode_chunk(0)
+
+    out, kc, vc = run(0)
+    for chunk in (512, 4160):
+        o2, kc2, vc2 = run(chunk)
+        diff = (out.float() - o2.float()).abs()
+        assert float(diff.max()) <= 1e-2 and float(diff.mean()) <= 1e-3, "split size %d" % chunk
+        assert torch.equal(kc.view(torch.int16), kc2.view(torch.int16))      # the append does not depend on it
+    # a KV-head shard (heads 2..3 and their query heads) of the same call
+    g = H // kvh
+    sl = slice(2, 4)
+    d_s = ops.make_desc(dt, batch, 2 * g, 2, 1, max_pos, layout="head", is_neox=neox)
+    d_s.total_kv_len = desc.total_kv_len
+    kc_s, vc_s = kc0[:, sl].contiguous(), vc0[:, sl].contiguous()
+    q_s = q.view(batch, H, D)[:, 2 * g:4 * g].reshape(batch, -1).contiguous()
+    k_s = k.view(batch, kvh, D)[:, sl].reshape(batch, -1).contiguous()
+    v_s = v.view(batch, kvh, D)[:, sl].reshape(batch, -1).contiguous()
+    ws_bytes = ops.gpu_attn_decode_workspace_bytes(d_s, mx)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    o_s = torch.empty((batch, 2 * g * D), dtype=torch.bfloat16, device="cuda")
+    ops.gpu_attn_decode_layer(d_s, o_s, None, None, q_s, k_s, v_s, kc_s, vc_s, table, lens_d, None, True, mx, ws, ws_bytes)
+    torch.cuda.synchronize()
+    diff = (o_s.float() - out.view(batch, H, D)[:, 2 * g:4 * g].reshape(batch, -1).float()).abs()
+    assert float(diff.max()) <= 1e-2 and float(diff.mean()) <= 1e-3
+    # the oracle on a sample of sequences, all heads
+    order = np.argsort(lens)
+    q_h, k_h, v_h = host(q), host(k), host(v)
+    for b in (int(order[0]), int(order[21]), int(order[42]), int(order[-1])):
+        L = int(lens[b])
+        kcb = host(kc0[b, :, :L + 1]).transpose(1, 0, 2).reshape(L + 1, kvh * D).copy()
+        vcb = host(vc0[b, :, :L + 1]).transpose(1, 0, 2).reshape(L + 1, kvh * D).copy()
+        q_r = orc.rope_single_layer(q_h[b:b + 1], table_np, L, H, neox, dt)
+        k_r = orc.rope_single_layer(k_h[b:b + 1], table_np, L, kvh, neox, dt)
+        orc.kv_append(kcb, vcb, k_r, v_h[b:b + 1], L, kvh, D)
+        gold = orc.attn(q_r, kcb, vcb, 1, L + 1, L, g, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
+        assert_parity(host(out[b]), gold[0], dt, "sequence %d, length %d" % (b, L))
+        assert np.array_equal(host(kc[b, :, L]).reshape(-1), k_r.reshape(-1))       # appended rows: the oracle's bits
+        assert np.array_equal(host(vc[b, :, L]).reshape(-1), v_h[b])
