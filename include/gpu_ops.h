@@ -369,6 +369,8 @@ int gpu_attn_set_prefill_kernel(int which);
  * bounded to about a second, after which the kernel records a code here, ends
  * normally and leaves the context usable.  Read it after synchronising. */
 int gpu_ops_kernel_status(void);
+/* Resets that status to 0 (call with no kernel of the library in flight on the device). */
+int gpu_ops_clear_kernel_status(void);
 
 /* Number of kernels launched by this library on the calling thread since the
  * last call with reset != 0. */

@@ -600,6 +600,11 @@ int *kernel_error_word_dev() {
   return dev;
 }
 
+void attn_clear_error_status() {
+  int *w = tc5::error_word();
+  if (w) *reinterpret_cast<volatile int *>(w) = 0;
+}
+
 int attn_tc5_error_status() {
   int *w = tc5::error_word();
   return w ? *reinterpret_cast<volatile int *>(w) : 0;

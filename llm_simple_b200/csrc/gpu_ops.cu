@@ -835,6 +835,11 @@ int gpu_attn_set_prefill_kernel(int which) {
 
 int gpu_ops_kernel_status(void) { return attn_tc5_error_status(); }
 
+int gpu_ops_clear_kernel_status(void) {
+  attn_clear_error_status();
+  return GPU_OPS_OK;
+}
+
 long gpu_ops_launch_count(int reset) {
   const long n = g_launches;
   if (reset) g_launches = 0;

@@ -132,6 +132,7 @@ cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStrea
 cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream);
 // Non-zero once a bounded wait inside a kernel on the current device has given up.
 int attn_tc5_error_status();
+void attn_clear_error_status();
 // Device address of that status word (host-mapped), or nullptr.
 int *kernel_error_word_dev();
 

@@ -27,7 +27,7 @@ EXPORTS = [
     "gpu_attn_decode_xchg_layer",
     "gpu_peer_buffer_alloc", "gpu_peer_buffer_open", "gpu_peer_buffer_close", "gpu_peer_buffer_free",
     "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel",
-    "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status",
+    "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status", "gpu_ops_clear_kernel_status",
 ]
 
 
@@ -339,6 +339,10 @@ def gpu_attn_set_decode_chunk(positions):
 
 def gpu_attn_set_prefill_kernel(which):
     _check(lib().gpu_attn_set_prefill_kernel(which))
+
+
+def gpu_ops_clear_kernel_status():
+    _check(lib().gpu_ops_clear_kernel_status())
 
 
 def gpu_ops_kernel_status():
