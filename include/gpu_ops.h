@@ -228,6 +228,49 @@ int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const vo
 size_t gpu_attn_decode_workspace_bytes(const gpu_attn_desc *desc, int max_kv_len);
 
 /* ------------------------------------------------------------------------
+ * Planned decode.  The reference's generation loop knows every cache length on
+ * the host (InferenceCtx::cur_pos / prev_pos, src/model_base.hpp:40-48, passed
+ * to the operators as the host integers m, n, offset); with a batch of
+ * sequences the host passes them as an array and the library cuts the step's
+ * work ONCE: all (sequence, KV head) caches laid end to end in 64-position
+ * tiles, one contiguous equally expensive share per CTA.  The plan is the same
+ * for every layer of the step.  The planned entry point runs the same fused
+ * step as gpu_attn_decode_layer on persistent CTAs whose K/V tiles arrive by
+ * TMA, so that the SMs finish together whatever the individual lengths are.
+ *
+ *   1. gpu_attn_decode_plan(desc, kv_len_host, append_new, 0, plan_host, bytes)
+ *      fills plan_host (host memory of gpu_attn_decode_plan_bytes(desc, 0) bytes;
+ *      pinned if it is to be copied asynchronously);
+ *   2. the caller copies gpu_attn_decode_plan_size(plan_host) bytes to device
+ *      memory (16-byte aligned), ordered before the layers on the stream;
+ *   3. gpu_attn_decode_planned_layer(...) once per layer, with scratch of
+ *      gpu_attn_decode_plan_workspace_bytes(plan_host) bytes.
+ * Only desc->batch, n_heads, n_kv_heads matter to the plan.  n_ctas: 0 = three
+ * quarters of the CTAs the current device holds at once (the rest of the slots
+ * lets the next call's CTAs move in early); a positive value (<= 1024) fixes it.
+ * ------------------------------------------------------------------------ */
+size_t gpu_attn_decode_plan_bytes(const gpu_attn_desc *desc, int n_ctas);
+int gpu_attn_decode_plan(const gpu_attn_desc *desc, const int32_t *kv_len_host, int append_new, int n_ctas,
+                         void *plan_host, size_t plan_bytes);
+size_t gpu_attn_decode_plan_size(const void *plan_host);
+size_t gpu_attn_decode_plan_workspace_bytes(const void *plan_host);
+
+/* One fused decode step driven by a plan: arguments as gpu_attn_decode_layer,
+ * with the lengths, append_new and the bound taken from the plan (plan_host: the
+ * host copy, read during the call; plan_dev: the device copy, read by the
+ * kernels; one upload serves every layer of the step).  pages: NULL for a flat cache, else the page description and
+ * k_cache / v_cache are the pools.  Sequences with an empty cache and no new
+ * token get a zero output (log-sum-exp -inf).  Honours
+ * gpu_attn_set_decode_early_prefetch, whose condition then also covers the
+ * device copy of the plan and the page table. */
+int gpu_attn_decode_planned_layer(const gpu_attn_desc *desc, const struct gpu_kv_pages *pages,
+                                  const void *plan_host, const void *plan_dev, void *out,
+                                  float *o_partial, float *lse_partial, const void *q_in,
+                                  const void *k_in, const void *v_in, void *k_cache, void *v_cache,
+                                  const void *freqs_cis_dev, const int32_t *rope_pos_dev,
+                                  void *workspace, size_t workspace_bytes, gpu_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Cross-device split-KV decode: exchange and merge of the ranks' partials in
  * ONE kernel over NVLink peer memory (plain peer stores, system-scope fence,
  * flags; no collective library call).  The reference is single-device and has

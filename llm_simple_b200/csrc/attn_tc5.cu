@@ -34,6 +34,7 @@
 // normal end (TMEM is freed) instead of spinning.
 #include "kernels.h"
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <cuda.h>
 #include <mutex>
@@ -42,6 +43,8 @@
 namespace b200attn {
 
 namespace tc5 {
+
+using namespace tma;
 
 constexpr int kBM = 128;            // query rows per tile; two tiles per CTA
 constexpr int kBN = 128;            // key positions per tile
@@ -61,55 +64,6 @@ constexpr float kRescaleThreshold = 8.0f;        // log2 domain
 // barrier slots (8 bytes each) inside the barrier block; X = 0 (tile A) or 1 (tile B)
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
        BAR_ODONE = 13, BAR_PHALF = 15, BAR_QB = 17, BAR_COUNT = 18 };
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-
-// Bounded wait.  Returns false (and raises the flags) when the phase has not
-// completed within ~2e9 cycles, or at once when another waiter already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          int *error_flag, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > 2000000000LL) {
-        *abort_flag = 1;
-        *reinterpret_cast<volatile int *>(error_flag) = code;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2,
-                                            int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -308,7 +262,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar(BAR_PHALF + s), 128);
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_barrier_init();
     // The first loads leave before TMEM is allocated and the other warps are released, so
     // that their latency (about 2500 cycles from a cold start) overlaps the set-up: Q_A and
     // the first K tile (what the first MMAs need), then the first V tile, then Q_B.
@@ -556,24 +510,6 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 4-D map over (d, dim1, dim2, dim3) with a box of 64 x box1 x box2 x 1 elements
-bool make_map(CUtensorMap *map, bool bf16, const void *base, uint64_t n1, uint64_t n2, uint64_t n3, long s1, long s2,
-              long s3, uint32_t box1, uint32_t box2) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  auto fix = [](long s) { return static_cast<cuuint64_t>(s > 0 ? s : 128) * 2; }; // bytes; unit extents may carry stride 0
-  cuuint64_t dims[4] = {128, n1, n2, n3};
-  cuuint64_t strides[3] = {fix(s1), fix(s2), fix(s3)};
-  cuuint32_t box[4] = {64, box1, box2, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  for (int i = 0; i < 3; ++i)
-    if (strides[i] % 16 || strides[i] >= (1ull << 40)) return false;
-  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 // device word the kernels raise when a bounded wait gives up; one per device
 int *error_word() {
   static std::mutex mu;
@@ -591,7 +527,30 @@ int *error_word() {
   return words[dev];
 }
 
+// 4-D map over (d, dim1, dim2, dim3) with a box of 64 x box1 x box2 x 1 elements
+bool make_tensor_map_4d_impl(CUtensorMap *map, bool bf16, const void *base, uint64_t n1, uint64_t n2, uint64_t n3, long s1, long s2,
+              long s3, uint32_t box1, uint32_t box2) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  auto fix = [](long s) { return static_cast<cuuint64_t>(s > 0 ? s : 128) * 2; }; // bytes; unit extents may carry stride 0
+  cuuint64_t dims[4] = {128, n1, n2, n3};
+  cuuint64_t strides[3] = {fix(s1), fix(s2), fix(s3)};
+  cuuint32_t box[4] = {64, box1, box2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16 || strides[i] >= (1ull << 40)) return false;
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 } // namespace tc5
+
+bool make_tensor_map_4d(CUtensorMap *map, bool bf16, const void *base, uint64_t n1, uint64_t n2, uint64_t n3, long s1,
+                        long s2, long s3, uint32_t box1, uint32_t box2) {
+  return tc5::make_tensor_map_4d_impl(map, bf16, base, n1, n2, n3, s1, s2, s3, box1, box2);
+}
 
 int *kernel_error_word_dev() {
   int *w = tc5::error_word();
@@ -615,20 +574,20 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   const AttnGeom &g = p.g;
   CUtensorMap mq, mk, mv, mk_tail, mv_tail;
   // q: (d, head, token, seq); k/v: (d, pos, kv_head, seq), or (d, pos in page, kv_head, page) over a pool
-  if (!make_map(&mq, bf16, p.q, g.n_heads, p.m, g.batch, kHeadDim, g.q_tok, g.q_seq, 1, kBM)) return cudaErrorNotSupported;
+  if (!make_tensor_map_4d(&mq, bf16, p.q, g.n_heads, p.m, g.batch, kHeadDim, g.q_tok, g.q_seq, 1, kBM)) return cudaErrorNotSupported;
   if (p.pg.table) {
     const int page_size = 1 << p.pg.page_shift;
     if (page_size < kBN) return cudaErrorNotSupported; // a K / V tile of 128 positions must lie inside one page
     const uint64_t n_pages = static_cast<uint64_t>(p.pg.n_pages);
     const uint64_t tail = static_cast<uint64_t>((p.n - 1) & (page_size - 1)) + 1;
-    if (!make_map(&mk, bf16, p.k_cache, page_size, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
-        !make_map(&mv, bf16, p.v_cache, page_size, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
-        !make_map(&mk_tail, bf16, p.k_cache, tail, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
-        !make_map(&mv_tail, bf16, p.v_cache, tail, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1))
+    if (!make_tensor_map_4d(&mk, bf16, p.k_cache, page_size, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
+        !make_tensor_map_4d(&mv, bf16, p.v_cache, page_size, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
+        !make_tensor_map_4d(&mk_tail, bf16, p.k_cache, tail, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1) ||
+        !make_tensor_map_4d(&mv_tail, bf16, p.v_cache, tail, g.n_kv_heads, n_pages, g.c_pos, g.c_head, p.pg.page_stride, kBN, 1))
       return cudaErrorNotSupported;
   } else {
-    if (!make_map(&mk, bf16, p.k_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1) ||
-        !make_map(&mv, bf16, p.v_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1))
+    if (!make_tensor_map_4d(&mk, bf16, p.k_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1) ||
+        !make_tensor_map_4d(&mv, bf16, p.v_cache, p.n, g.n_kv_heads, g.batch, g.c_pos, g.c_head, g.c_seq, kBN, 1))
       return cudaErrorNotSupported;
     mk_tail = mk;
     mv_tail = mv;

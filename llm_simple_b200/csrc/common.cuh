@@ -98,6 +98,15 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
   return static_cast<uint32_t>(row * kRowBytes + ((chunk ^ (row & 7)) << 4));
 }
 
+// Layout of a K/V tile written by TMA with the 128-byte swizzle: two half tiles of
+// [rows][64 elements] (128-byte rows), the second HALF_BYTES after the first; the 16-byte chunk
+// c of a 128-byte row sits at chunk position c ^ (row & 7).  HALF_BYTES == 0 selects the
+// 256-byte-row layout above.
+template <int HALF_BYTES> __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  if (HALF_BYTES == 0) return swz_off(row, chunk);
+  return static_cast<uint32_t>((chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -174,7 +183,8 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qa)[8][4], uint32_t q_sm
 //   lim0/lim1: per-row causal limits (positions >= lim are masked) of the
 //              thread's two rows
 //   scale_log2: softmax scale * log2(e)
-template <typename T, int NT>
+//   HALF_BYTES: layout of the K / V tiles (see tile_off)
+template <typename T, int NT, int HALF_BYTES = 0>
 __device__ __forceinline__ void warp_tile(WarpAcc &acc, const uint32_t (&qa)[8][4], uint32_t k_smem,
                                           uint32_t v_smem, int krow0, int col0, int col_end, int lim0,
                                           int lim1, float scale_log2, int lane) {
@@ -191,7 +201,7 @@ __device__ __forceinline__ void warp_tile(WarpAcc &acc, const uint32_t (&qa)[8][
     for (int np = 0; np < NT / 2; ++np) {
       uint32_t kb[4];
       const int row = krow0 + np * 16 + (j >> 1) * 8 + r;
-      ldmatrix_x4(kb, k_smem + swz_off(row, 2 * ks + (j & 1)));
+      ldmatrix_x4(kb, k_smem + tile_off<HALF_BYTES>(row, 2 * ks + (j & 1)));
       mma_16816<T>(s[2 * np], qa[ks], kb[0], kb[1]);
       mma_16816<T>(s[2 * np + 1], qa[ks], kb[2], kb[3]);
     }
@@ -248,7 +258,7 @@ __device__ __forceinline__ void warp_tile(WarpAcc &acc, const uint32_t (&qa)[8][
 #pragma unroll
     for (int dp = 0; dp < 8; ++dp) {
       uint32_t vb[4];
-      ldmatrix_x4_trans(vb, v_smem + swz_off(row, 2 * dp + (j >> 1)));
+      ldmatrix_x4_trans(vb, v_smem + tile_off<HALF_BYTES>(row, 2 * dp + (j >> 1)));
       mma_16816<T>(acc.o[2 * dp], pa[kp], vb[0], vb[1]);
       mma_16816<T>(acc.o[2 * dp + 1], pa[kp], vb[2], vb[3]);
     }

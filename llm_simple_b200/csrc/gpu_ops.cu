@@ -4,6 +4,7 @@
 #include "gpu_ops.h"
 #include "kernels.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -721,6 +722,124 @@ int gpu_attn_decode_paged_layer(const gpu_attn_desc *desc, const gpu_kv_pages *p
   if (!pages) return fail(GPU_OPS_E_INVALID, "null page description");
   return decode_common(desc, pages, out, nullptr, nullptr, q_in, k_in, v_in, k_pool, v_pool, freqs_cis_dev, kv_len_dev,
                        nullptr, append_new, max_kv_len, workspace, workspace_bytes, stream);
+}
+
+// ---- planned decode ---------------------------------------------------------------
+namespace {
+constexpr int kPlanMaxCtas = 1024;
+
+const PlanHeader *plan_header(const void *plan_host) {
+  const PlanHeader *h = static_cast<const PlanHeader *>(plan_host);
+  return (h && h->magic == kPlanMagic) ? h : nullptr;
+}
+} // namespace
+
+size_t gpu_attn_decode_plan_bytes(const gpu_attn_desc *desc, int n_ctas) {
+  if (!desc || n_ctas < 0 || n_ctas > kPlanMaxCtas) return 0;
+  return decode_plan_capacity(desc->batch, desc->n_kv_heads, n_ctas > 0 ? n_ctas : kPlanMaxCtas);
+}
+
+int gpu_attn_decode_plan(const gpu_attn_desc *desc, const int32_t *kv_len_host, int append_new, int n_ctas,
+                         void *plan_host, size_t plan_bytes) {
+  if (int rc = check_desc(desc)) return rc;
+  if (!kv_len_host || !plan_host) return fail(GPU_OPS_E_INVALID, "null pointer");
+  if (desc->n_heads / desc->n_kv_heads > 16)
+    return fail(GPU_OPS_E_UNSUPPORTED, "group size %d: at most 16 query heads per KV head", desc->n_heads / desc->n_kv_heads);
+  if (n_ctas < 0 || n_ctas > kPlanMaxCtas) return fail(GPU_OPS_E_INVALID, "n_ctas %d (0 .. %d)", n_ctas, kPlanMaxCtas);
+  if (n_ctas == 0) {
+    // Three quarters of what the current device holds at once: consecutive calls are launched as
+    // programmatic dependents, and the free quarter lets the next call's first CTAs move in and
+    // fetch their first tiles while this call still streams (measured on B200, 296 slots: 222 CTAs
+    // beat 296 by 0 - 3 % at every size from 87 MB to 694 MB per call).
+    const int slots = decode_planned_max_ctas();
+    if (slots <= 0) return fail(GPU_OPS_E_CUDA, "no current CUDA device to size the plan for");
+    n_ctas = std::min(kPlanMaxCtas, std::max(1, slots * 3 / 4));
+  }
+  for (int b = 0; b < desc->batch; ++b)
+    if (kv_len_host[b] < 0) return fail(GPU_OPS_E_INVALID, "kv_len[%d] = %d", b, kv_len_host[b]);
+  const size_t used = build_decode_plan(plan_host, plan_bytes, kv_len_host, desc->batch, desc->n_kv_heads,
+                                        desc->n_heads / desc->n_kv_heads, append_new, n_ctas);
+  if (!used) return fail(GPU_OPS_E_WORKSPACE, "plan buffer of %zu bytes is too small", plan_bytes);
+  return GPU_OPS_OK;
+}
+
+size_t gpu_attn_decode_plan_size(const void *plan_host) {
+  const PlanHeader *h = plan_header(plan_host);
+  return h ? static_cast<size_t>(h->total_bytes) : 0;
+}
+
+size_t gpu_attn_decode_plan_workspace_bytes(const void *plan_host) {
+  const PlanHeader *h = plan_header(plan_host);
+  return h ? static_cast<size_t>(h->n_slots) * h->group * (128 + 1) * sizeof(float) : 0;
+}
+
+int gpu_attn_decode_planned_layer(const gpu_attn_desc *desc, const gpu_kv_pages *pages, const void *plan_host,
+                                  const void *plan_dev, void *out, float *o_partial, float *lse_partial,
+                                  const void *q_in, const void *k_in, const void *v_in, void *k_cache, void *v_cache,
+                                  const void *freqs_cis_dev, const int32_t *rope_pos_dev, void *workspace,
+                                  size_t workspace_bytes, gpu_stream_t stream) {
+  if (int rc = check_desc(desc)) return rc;
+  KvPaging pg;
+  if (int rc = paging_from(pages, &pg)) return rc;
+  const PlanHeader *h = plan_header(plan_host);
+  if (!h || !plan_dev) return fail(GPU_OPS_E_INVALID, "not a decode plan");
+  const int group = desc->n_heads / desc->n_kv_heads;
+  if (h->batch != desc->batch || h->n_kv_heads != desc->n_kv_heads || h->group != group)
+    return fail(GPU_OPS_E_INVALID, "plan was built for batch %d, %d KV heads, group %d", h->batch, h->n_kv_heads, h->group);
+  if (!q_in || !k_cache || !v_cache || !freqs_cis_dev) return fail(GPU_OPS_E_INVALID, "null tensor pointer");
+  if ((o_partial == nullptr) != (lse_partial == nullptr))
+    return fail(GPU_OPS_E_INVALID, "o_partial and lse_partial go together");
+  if (!out && !o_partial) return fail(GPU_OPS_E_INVALID, "no output given");
+  if (h->append && (!k_in || !v_in)) return fail(GPU_OPS_E_INVALID, "the plan appends a token: k_in and v_in are needed");
+  if (!aligned16(out) || !aligned16(q_in) || !aligned16(k_in) || !aligned16(v_in) || !aligned16(k_cache) ||
+      !aligned16(v_cache) || !aligned16(freqs_cis_dev) || !aligned16(workspace) || !aligned16(plan_dev) ||
+      !aligned16(o_partial))
+    return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  const size_t need = gpu_attn_decode_plan_workspace_bytes(plan_host);
+  if (need && (!workspace || workspace_bytes < need))
+    return fail(GPU_OPS_E_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  if (pages && h->max_total > 0) {
+    const long entries = (static_cast<long>(h->max_total) + pages->page_size - 1) / pages->page_size;
+    if (entries > pages->table_stride)
+      return fail(GPU_OPS_E_INVALID, "page table rows hold %d entries, %ld needed", pages->table_stride, entries);
+  }
+  PlannedDecodeParams p{};
+  p.g = geom_from_desc(desc);
+  p.out = o_partial ? nullptr : out;
+  p.o_partial = o_partial;
+  p.lse_partial = lse_partial;
+  p.q = q_in;
+  p.k_new = k_in;
+  p.v_new = v_in;
+  p.kv_in_seq = desc->kv_in_seq_stride;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.freqs_cis = static_cast<const float *>(freqs_cis_dev);
+  p.rope_pos_dev = rope_pos_dev;
+  p.is_neox = desc->is_neox_style ? 1 : 0;
+  p.scale_log2 = scale_log2_of(desc->head_dim);
+  p.plan = static_cast<const unsigned char *>(plan_dev);
+  p.n_ctas = h->n_ctas;
+  p.n_groups = h->n_groups;
+  p.n_slots = h->n_slots;
+  p.max_total = h->max_total > 0 ? h->max_total : 1;
+  p.off_cta_begin = h->off_cta_begin;
+  p.off_items = h->off_items;
+  p.off_groups = h->off_groups;
+  p.max_parts = h->max_parts;
+  p.ws_o = static_cast<float *>(workspace);
+  p.ws_lse = p.ws_o ? p.ws_o + static_cast<size_t>(h->n_slots) * group * 128 : nullptr;
+  p.pg = pg;
+  p.early_kv = g_decode_early.load();
+  p.error_flag = kernel_error_word_dev();
+  if (!p.error_flag) return fail(GPU_OPS_E_CUDA, "no status word");
+  int launches = 0;
+  cudaError_t e = launch_attn_decode_planned(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream), &launches);
+  g_launches += launches;
+  if (e == cudaErrorNotSupported)
+    return fail(GPU_OPS_E_UNSUPPORTED, "the cache strides cannot be described by a TMA tensor map");
+  if (e != cudaSuccess) return cuda_fail(e, "planned decode launch");
+  return GPU_OPS_OK;
 }
 
 static int merge_parts(void *out, const float *o_parts, const float *lse_parts, long stride_o, long stride_lse,

@@ -113,6 +113,81 @@ struct MergeParams {
 
 cudaError_t launch_attn_merge(const MergeParams &p, bool bf16, cudaStream_t stream);
 
+// ---- planned decode (persistent CTAs, TMA-fed ring) -------------------------------
+// The host cuts the step's work -- every (sequence, KV head) cache laid end to end in tiles of
+// 64 positions -- into one contiguous, equally expensive share per CTA and stores the result as a
+// "plan": a blob of 32-bit words that is identical in host and device memory.
+//   header (PlanHeader) | cta_begin[n_ctas + 1] | items[n_items] | groups[n_groups]
+// CTA c works through items [cta_begin[c], cta_begin[c + 1]).  A cache that was cut leaves one
+// partial result per piece in consecutive scratch slots; its pieces form a merge group.
+constexpr uint32_t kPlanMagic = 0x504c414eu; // "PLAN"
+
+struct PlanHeader { // 64 bytes
+  uint32_t magic;
+  int32_t n_ctas, n_items, n_groups;
+  int32_t n_slots;       // partial-result slots the plan uses (scratch = n_slots * group * 129 floats)
+  int32_t batch, n_kv_heads, group;
+  int32_t append;        // 1: every sequence gets its new token appended at kv_len[b]
+  int32_t max_total;     // max over the batch of kv_len[b] + append
+  int32_t off_cta_begin, off_items, off_groups; // byte offsets from the start of the blob
+  int32_t total_bytes;
+  int32_t total_tiles;
+  int32_t max_parts;     // pieces of the most-cut cache
+};
+static_assert(sizeof(PlanHeader) == 64, "plan header layout");
+
+struct PlanItem { // 32 bytes: one contiguous piece of one (sequence, KV head) cache
+  int32_t b, kvh;
+  int32_t pos0, pos_end; // cache positions [pos0, pos_end); pos0 a multiple of 64; the new token counts when it falls inside
+  int32_t len_old;       // tokens cached before this step
+  int32_t slot;          // >= 0: the piece is one of several, its partial result goes to this slot; -1: it is the whole cache
+  int32_t has_new;       // 1: the piece contains position len_old, the token appended by this step
+  int32_t reserved;
+};
+static_assert(sizeof(PlanItem) == 32, "plan item layout");
+
+struct PlanGroup { // 16 bytes: the pieces of one cut (sequence, KV head) cache, slots first_slot .. first_slot + n_parts - 1
+  int32_t first_slot, n_parts;
+  int32_t b, kvh;
+};
+static_assert(sizeof(PlanGroup) == 16, "plan group layout");
+
+struct PlannedDecodeParams {
+  AttnGeom g;
+  void *out;            // dtype [batch][H*128] (strided), or NULL with the partial pair below
+  float *o_partial;     // fp32 [batch*H][128] + lse_partial (natural log), for a merge across devices
+  float *lse_partial;
+  const void *q;        // raw query rows, rotated here
+  const void *k_new;    // raw new-token K / V (plan built with append)
+  const void *v_new;
+  long kv_in_seq;
+  void *k_cache;
+  void *v_cache;
+  const float *freqs_cis;
+  const int32_t *rope_pos_dev; // table row per sequence, or NULL: the cached length
+  int is_neox;
+  float scale_log2;
+  const unsigned char *plan;   // the blob in device memory
+  int n_ctas, n_groups, n_slots, max_total, max_parts;
+  int off_cta_begin, off_items, off_groups;
+  float *ws_o;          // [n_slots][group][128] fp32 (normalised partial outputs)
+  float *ws_lse;        // [n_slots][group] (log2 domain)
+  KvPaging pg;
+  int early_kv;         // 1: K/V tiles may be requested before the preceding kernels have finished
+  int *error_flag;
+};
+
+cudaError_t launch_attn_decode_planned(const PlannedDecodeParams &p, bool bf16, cudaStream_t stream, int *launches);
+
+// Host-side plan builder (decode_plan.cpp).  kv_len: tokens cached per sequence (host memory).
+// n_ctas: CTAs to cut the work for.  Returns the
+// number of bytes written to `blob`, or 0 if `capacity` is too small / the arguments are invalid.
+size_t decode_plan_capacity(int batch, int n_kv_heads, int n_ctas);
+size_t build_decode_plan(void *blob, size_t capacity, const int32_t *kv_len, int batch, int n_kv_heads, int group,
+                         int append, int n_ctas);
+// CTAs of attn_decode_tma_kernel that the current device can hold at once; 0 on failure.
+int decode_planned_max_ctas();
+
 // ---- general causal attention (mma.sync, any m/n/offset) -----------------------
 struct PrefillParams {
   AttnGeom g;

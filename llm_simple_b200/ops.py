@@ -21,7 +21,8 @@ EXPORTS = [
     "gpu_flash_attn_layer", "gpu_flash_attn_gqa_layer", "gpu_flash_attn_opt_prefill_layer",
     "gpu_rope_layer", "gpu_rope_single_layer", "gpu_split_qkv_layer", "gpu_rope_kv_append_layer",
     "gpu_qkv_rope_kv_append_layer", "gpu_bias_add_layer", "gpu_attn_prefill_layer",
-    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_rope_kv_append_paged_layer",
+    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_plan_bytes", "gpu_attn_decode_plan",
+    "gpu_attn_decode_plan_size", "gpu_attn_decode_plan_workspace_bytes", "gpu_attn_decode_planned_layer", "gpu_rope_kv_append_paged_layer",
     "gpu_attn_decode_paged_layer", "gpu_attn_prefill_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_attn_xchg_buffer_bytes", "gpu_attn_xchg_local_slot", "gpu_attn_xchg_merge_layer",
     "gpu_attn_decode_xchg_layer",
@@ -117,6 +118,15 @@ def lib():
         L.gpu_attn_decode_layer.argtypes = [dp, vp, f32p, f32p] + [vp] * 6 + [i32p, i32p, i, i, vp,
                                                                                ctypes.c_size_t, vp]
         L.gpu_attn_decode_layer_noalloc.argtypes = [dp] + [vp] * 7 + [i32p, i32p, i, i, vp]
+        L.gpu_attn_decode_plan_bytes.argtypes = [dp, i]
+        L.gpu_attn_decode_plan_bytes.restype = ctypes.c_size_t
+        L.gpu_attn_decode_plan.argtypes = [dp, i32p, i, i, vp, ctypes.c_size_t]
+        L.gpu_attn_decode_plan_size.argtypes = [vp]
+        L.gpu_attn_decode_plan_size.restype = ctypes.c_size_t
+        L.gpu_attn_decode_plan_workspace_bytes.argtypes = [vp]
+        L.gpu_attn_decode_plan_workspace_bytes.restype = ctypes.c_size_t
+        L.gpu_attn_decode_planned_layer.argtypes = [dp, pp, vp, vp, vp, f32p, f32p] + [vp] * 6 + [i32p, vp,
+                                                                                                 ctypes.c_size_t, vp]
         L.gpu_attn_decode_workspace_bytes.argtypes = [dp, i]
         L.gpu_attn_decode_workspace_bytes.restype = ctypes.c_size_t
         L.gpu_attn_merge_lse_layer.argtypes = [vp, f32p, f32p, i, i, i, i, vp]
@@ -257,6 +267,60 @@ def gpu_attn_decode_layer(desc, out, o_partial, lse_partial, q_in, k_in, v_in, k
                                        _ptr(freqs_cis), _ptr(kv_len_dev), _ptr(rope_pos_dev),
                                        int(bool(append_new)), max_kv_len, _ptr(workspace), workspace_bytes,
                                        _stream(stream)))
+
+
+class DecodePlan:
+    """Work partition of one decode step (gpu_attn_decode_plan): built from the
+    host's cache lengths, the same for every layer of the step.  `host` is the
+    blob as a numpy uint8 array; upload() copies it into a CUDA tensor."""
+
+    def __init__(self, desc, kv_len_host, append_new, n_ctas=0):
+        import numpy as np
+        cap = int(lib().gpu_attn_decode_plan_bytes(ctypes.byref(desc), n_ctas))
+        if cap == 0:
+            raise GpuOpsError("gpu_attn_decode_plan_bytes: invalid arguments")
+        lens = np.ascontiguousarray(np.asarray(kv_len_host, dtype=np.int32))
+        buf = np.zeros(cap, dtype=np.uint8)
+        _check(lib().gpu_attn_decode_plan(ctypes.byref(desc), lens.ctypes.data, int(bool(append_new)), n_ctas,
+                                          buf.ctypes.data, cap))
+        self.size = int(lib().gpu_attn_decode_plan_size(buf.ctypes.data))
+        self.host = buf[:self.size].copy()
+        self.workspace_bytes = int(lib().gpu_attn_decode_plan_workspace_bytes(self.host.ctypes.data))
+        self.dev = None
+
+    @property
+    def header(self):
+        """The plan header as a dict of its 32-bit fields."""
+        import numpy as np
+        w = self.host[:64].view(np.int32)
+        names = ["magic", "n_ctas", "n_items", "n_groups", "n_slots", "batch", "n_kv_heads", "group", "append",
+                 "max_total", "off_cta_begin", "off_items", "off_groups", "total_bytes", "total_tiles", "max_parts"]
+        return dict(zip(names, (int(x) for x in w)))
+
+    def tables(self):
+        """(cta_begin, items [n][8], groups [n][4]) as numpy int32 arrays (for tests)."""
+        import numpy as np
+        h = self.header
+        words = self.host.view(np.int32)
+        cb = words[h["off_cta_begin"] // 4: h["off_cta_begin"] // 4 + h["n_ctas"] + 1]
+        it = words[h["off_items"] // 4: h["off_items"] // 4 + 8 * h["n_items"]].reshape(-1, 8)
+        mg = words[h["off_groups"] // 4: h["off_groups"] // 4 + 4 * h["n_groups"]].reshape(-1, 4)
+        return cb, it, mg
+
+    def upload(self, device=None):
+        import torch
+        self.dev = torch.from_numpy(self.host).to(device if device is not None else "cuda")
+        return self.dev
+
+
+def gpu_attn_decode_planned_layer(desc, pages, plan, out, o_partial, lse_partial, q_in, k_in, v_in, k_cache, v_cache,
+                                  freqs_cis, rope_pos_dev, workspace, workspace_bytes, stream=None):
+    """One fused decode step driven by a DecodePlan (upload() it first)."""
+    _check(lib().gpu_attn_decode_planned_layer(ctypes.byref(desc), ctypes.byref(pages) if pages is not None else None,
+                                               plan.host.ctypes.data, _ptr(plan.dev), _ptr(out), _ptr(o_partial),
+                                               _ptr(lse_partial), _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(k_cache),
+                                               _ptr(v_cache), _ptr(freqs_cis), _ptr(rope_pos_dev), _ptr(workspace),
+                                               workspace_bytes, _stream(stream)))
 
 
 def gpu_attn_decode_layer_noalloc(desc, out, q_in, k_in, v_in, k_cache, v_cache, freqs_cis, kv_len_dev,
