@@ -37,6 +37,16 @@ void gpu_allocator_use_host_backend(int on);
  * value to bf16.  Host memory in, host memory out. */
 void gpu_init_freq_cis(float *host_out, int head_dim, int max_seq_len, float theta, int dt);
 
+/* ---- KV cache layout: the three cache strides of *desc for a per-layer cache
+ * of max_seq_len positions per sequence.  cache_layout 0 = token-major
+ * [seq][pos][kv_head][D], the reference's (src/llama2_layer_npu.cpp:1148-1149
+ * allocates n_kv_heads * D * max_seq_len elements, :830-843 appends at byte
+ * offset prev_pos * n_kv_heads * D * 2); 1 = head-major [seq][kv_head][pos][D].
+ * Returns the elements one sequence's K (or V) cache occupies, 0 on bad
+ * arguments. ---- */
+size_t gpu_kv_cache_layout(gpu_attn_desc *desc, int cache_layout, int n_kv_heads, int max_seq_len,
+                           int head_dim);
+
 /* ---- attention section of a transformer layer.  kind 0: Llama-2
  * (Llamma2TransformerLayerNPUImpl, src/llama2_layer_npu.cpp:283-374: MHA, fp16);
  * kind 1: Qwen2 (Qwen2TransformerLayerNPUImpl, :780-869: GQA).  The layer owns
@@ -71,6 +81,21 @@ int gpu_attention_layer_decode_ragged(void *layer, void *out, const void *q, con
  * unknown).  While set, decode calls use it. */
 int gpu_attention_layer_set_shared_lens(void *layer, const int32_t *kv_len_dev, int max_kv_len,
                                         long total_kv_len);
+
+/* State that a model prepares once per decode step for all its layers: the work
+ * partition of the step (gpu_attn_decode_plan) for the sequences' cache lengths
+ * -- which the host knows, as the reference's generation loop knows cur_pos /
+ * prev_pos (src/model_base.hpp:40-48) -- with its device copy and the scratch of
+ * the planned decode kernel.  prepare() enqueues the upload on `stream` without
+ * waiting for it; the layers' calls of the step follow on the same stream.
+ * While a step is set on a layer, its decode calls run
+ * gpu_attn_decode_planned_layer on it and ignore their own length arguments.
+ * Call with the device current that will run the layers. */
+void *gpu_decode_step_create(int max_batch, int n_heads, int n_kv_heads, int dt);
+void gpu_decode_step_destroy(void *step);
+int gpu_decode_step_prepare(void *step, const int32_t *kv_len_host, int batch, int append_new,
+                            gpu_stream_t stream);
+int gpu_attention_layer_set_shared_step(void *layer, void *step /* NULL unsets */);
 
 /* The same forward with HOST buffers: qkv_host [batch][cur_size][(n_heads +
  * 2 n_kv_heads)*D] (q, k, v columns of one packed projection row; pinned memory

@@ -207,17 +207,22 @@ int gpu_attn_decode_layer(const gpu_attn_desc *desc, void *out, float *o_partial
  * cudaMalloc's device-wide synchronisation.  They have no way to supply
  * gpu_attn_decode_layer's workspace.  This entry point
  * needs none: its split-KV scratch is a fixed 16 MiB array in the library's own
- * device image, held by every GPU that loads the library until the process
- * exits.  It calls no cudaMalloc / cudaFree and no allocating routine.
+ * device image.  It calls no cudaMalloc / cudaFree and no allocating routine.
  *   - Splits are always 512 positions; a call needs batch * n_heads *
  *     ceil(max_kv_len / 512) * 516 bytes of scratch and is rejected with
  *     GPU_OPS_E_WORKSPACE (nothing launched) when that exceeds 16 MiB.
- *   - The first call on each device looks up the array's device address (with
- *     that device current); make that first call before any stream capture.
+ *   - The array's device address is looked up on the first use per device (with
+ *     that device current), by gpu_attn_decode_noalloc_prepare() or by the first
+ *     call of the entry point.  With CUDA's lazy module loading that look-up is
+ *     also when the device takes the 16 MiB, which it then holds until the
+ *     process exits: do it at start-up, BEFORE the host reserves the rest of the
+ *     device memory and before any stream capture (or run with
+ *     CUDA_MODULE_LOADING=EAGER, which takes the memory when the library loads).
  *   - All calls on a device share the array, which keeps the previous call's
  *     contents; nothing in it needs clearing, but calls whose kernels overlap on
  *     the GPU race on it: order them on one stream or with events.
  * Arguments as gpu_attn_decode_layer, without the partial outputs and workspace. */
+int gpu_attn_decode_noalloc_prepare(void);
 int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const void *q_in,
                                   const void *k_in, const void *v_in, void *k_cache,
                                   void *v_cache, const void *freqs_cis_dev,
@@ -407,10 +412,20 @@ int gpu_attn_set_decode_chunk(int positions);
  * 2 = tcgen05 kernel.  Process-wide; for tests and measurements. */
 int gpu_attn_set_prefill_kernel(int which);
 
-/* 0, or the code of the first wait inside a kernel on the current device that
- * gave up: every device-side wait (mbarrier polls of the tcgen05 kernel) is
- * bounded to about a second, after which the kernel records a code here, ends
- * normally and leaves the context usable.  Read it after synchronising. */
+/* Which kernel served the calling thread's last prefill-shaped call: 1 = mma.sync
+ * kernel, 2 = tcgen05 kernel, 0 = none yet.  The automatic choice falls back to
+ * the mma.sync kernel when the tcgen05 kernel's tensor maps cannot describe a
+ * geometry (a stride that is no multiple of 16 bytes, pages below 128
+ * positions); a caller that counts on the faster kernel can check here. */
+int gpu_attn_last_prefill_kernel(void);
+
+/* 0, or the code a kernel on the current device recorded: every device-side
+ * wait (mbarrier polls, flags of other ranks) is bounded to about a second,
+ * after which the kernel stores a code (1 .. 39) here, ends normally and leaves
+ * the context usable; 40 = a sequence of gpu_attn_decode_layer was longer than
+ * max_kv_len, so that its last positions -- the new token among them -- were not
+ * covered (the output and cache of that sequence are wrong, nothing is read or
+ * written out of bounds).  Read it after synchronising. */
 int gpu_ops_kernel_status(void);
 /* Resets that status to 0 (call with no kernel of the library in flight on the device). */
 int gpu_ops_clear_kernel_status(void);

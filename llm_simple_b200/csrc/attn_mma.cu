@@ -16,6 +16,10 @@
 
 #include <limits.h>
 
+#include <mutex>
+#include <utility>
+#include <vector>
+
 namespace b200attn {
 
 namespace {
@@ -59,6 +63,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) attn_decode_kernel(DecodePa
   const int len_old = p.kv_len_dev ? p.kv_len_dev[b] : p.kv_len;
   const int total = len_old + (p.append ? 1 : 0);
   const int nsplit = max(1, (total + p.chunk - 1) / p.chunk);
+  // the grid was sized from the host's bound of the lengths: a longer sequence cannot be covered
+  // (its last positions, the new token among them, would be dropped) -- tell the host
+  if (split == 0 && nsplit > static_cast<int>(gridDim.x) && tid == 0 && p.error_flag)
+    *reinterpret_cast<volatile int *>(p.error_flag) = kStatusLengthBeyondBound;
   if (split >= nsplit) return;
   const int pos0 = split * p.chunk;
   const int pos_end = min(total, pos0 + p.chunk);
@@ -263,6 +271,7 @@ template <typename T> __global__ void __launch_bounds__(128) attn_merge_kernel(M
     const int total = (p.kv_len_dev ? p.kv_len_dev[b] : p.kv_len) + p.append;
     n_parts = max(1, (total + p.chunk - 1) / p.chunk);
   }
+  n_parts = min(n_parts, p.max_parts); // never read beyond the row's slots, whatever the length says
   const float to_log2 = p.lse_is_log2 ? 1.f : kLog2e;
   float M = -INFINITY;
   // part i of this row: (lse index, o index / 128)
@@ -402,8 +411,22 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_mma_kernel(PrefillParams 
 // ---------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------
+// The shared-memory opt-in is a property of (function, device): set it on the first launch of a
+// function on a device.  (Keyed on the function's address: the two instantiations of a kernel
+// template have the same pointer type.)
 template <typename K> static cudaError_t set_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  static std::mutex mu;
+  static std::vector<std::pair<const void *, int>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const std::pair<const void *, int> key(reinterpret_cast<const void *>(kernel), dev);
+  std::lock_guard<std::mutex> lk(mu);
+  for (const auto &d : done)
+    if (d == key) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.push_back(key);
+  return e;
 }
 
 // Launch with programmatic stream serialisation (programmatic dependent launch): the

@@ -37,6 +37,7 @@
 #include "tma.cuh"
 
 #include <cuda.h>
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -549,7 +550,30 @@ bool make_tensor_map_4d_impl(CUtensorMap *map, bool bf16, const void *base, uint
 
 bool make_tensor_map_4d(CUtensorMap *map, bool bf16, const void *base, uint64_t n1, uint64_t n2, uint64_t n3, long s1,
                         long s2, long s3, uint32_t box1, uint32_t box2) {
-  return tc5::make_tensor_map_4d_impl(map, bf16, base, n1, n2, n3, s1, s2, s3, box1, box2);
+  // the encoding depends on nothing but these arguments: keep the most recent ones per thread
+  constexpr int kCached = 32;
+  struct Entry {
+    TensorMapKey key;
+    CUtensorMap map;
+    bool used;
+  };
+  thread_local Entry cache[kCached] = {};
+  thread_local int next = 0;
+  TensorMapKey key{};
+  key.base = base, key.n1 = n1, key.n2 = n2, key.n3 = n3, key.s1 = s1, key.s2 = s2, key.s3 = s3;
+  key.box1 = box1, key.box2 = box2, key.bf16 = bf16 ? 1u : 0u;
+  for (int i = 0; i < kCached; ++i) {
+    if (cache[i].used && memcmp(&cache[i].key, &key, sizeof key) == 0) {
+      *map = cache[i].map;
+      return true;
+    }
+  }
+  if (!tc5::make_tensor_map_4d_impl(map, bf16, base, n1, n2, n3, s1, s2, s3, box1, box2)) return false;
+  cache[next].key = key;
+  cache[next].map = *map;
+  cache[next].used = true;
+  next = (next + 1) % kCached;
+  return true;
 }
 
 int *kernel_error_word_dev() {
@@ -610,16 +634,22 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   kp.table_stride = p.pg.table_stride;
   kp.page_shift = p.pg.page_shift;
   dim3 grid((p.m + 2 * kBM - 1) / (2 * kBM), g.n_heads, g.batch);
-  cudaError_t e;
-  if (bf16) {
-    e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+  // the shared-memory opt-in is a property of (function, device): set it on the first launch per device
+  static bool attr_set[2][64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool known = dev >= 0 && dev < 64;
+  if (!known || !attr_set[bf16 ? 1 : 0][dev]) {
+    e = bf16 ? cudaFuncSetAttribute(attn_prefill_tc5_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal)
+             : cudaFuncSetAttribute(attn_prefill_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return e;
-    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
-  } else {
-    e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    if (e != cudaSuccess) return e;
-    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
+    if (known) attr_set[bf16 ? 1 : 0][dev] = true;
   }
+  if (bf16)
+    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
+  else
+    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
   return cudaGetLastError();
 }
 

@@ -11,8 +11,13 @@
 // This one brings its own: a fixed array in device global memory that is part
 // of the library image.
 //
-// Cost and limit: every GPU that loads the library holds kNoAllocScratchBytes
-// (16 MiB) until the process exits, used or not.  The scratch holds, per query
+// Cost and limit: every GPU on which the array has been resolved holds
+// kNoAllocScratchBytes (16 MiB) until the process exits, used or not.  With CUDA's
+// lazy module loading the array is materialised -- and its 16 MiB taken -- when its
+// address is first looked up on a device, not when the library is loaded: a host
+// that hands all device memory to its own pool must make that first look-up
+// (gpu_attn_decode_noalloc_prepare, or a first call of the entry point) BEFORE it
+// reserves its memory, or run with CUDA_MODULE_LOADING=EAGER.  The scratch holds, per query
 // head and split, 128 fp32 partial outputs and one log-sum-exp, so a call needs
 // batch * n_heads * ceil(max_kv_len / 512) * 516 bytes; a call that needs more
 // is rejected with GPU_OPS_E_WORKSPACE before anything is launched.
@@ -74,6 +79,17 @@ int fail(int code, const char *msg) {
 } // namespace
 
 extern "C" {
+
+int gpu_attn_decode_noalloc_prepare(void) {
+  void *scratch = nullptr;
+  cudaError_t e = scratch_address(&scratch);
+  if (e != cudaSuccess) {
+    char msg[256];
+    snprintf(msg, sizeof msg, "cudaGetSymbolAddress of the scratch array: %s", cudaGetErrorString(e));
+    return fail(GPU_OPS_E_CUDA, msg);
+  }
+  return GPU_OPS_OK;
+}
 
 int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const void *q_in, const void *k_in,
                                   const void *v_in, void *k_cache, void *v_cache, const void *freqs_cis_dev,
@@ -148,12 +164,14 @@ int gpu_attn_decode_layer_noalloc(const gpu_attn_desc *desc, void *out, const vo
   p.chunk = kNoAllocChunk;
   p.max_splits = splits;
   p.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
+  p.error_flag = kernel_error_word_dev();
   if (splits > 1) {
     p.ws_o = static_cast<float *>(scratch);
     p.ws_lse = p.ws_o + rows * splits * 128;
   }
   int launches = 0;
   e = launch_attn_decode(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream), &launches);
+  add_launch_count(launches);
   if (e != cudaSuccess) {
     char msg[256];
     snprintf(msg, sizeof msg, "decode attention launch: %s", cudaGetErrorString(e));

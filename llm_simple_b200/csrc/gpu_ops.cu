@@ -20,6 +20,7 @@ namespace {
 
 thread_local std::string g_last_error;
 thread_local long g_launches = 0;
+thread_local int g_last_prefill_kernel = 0; // 1 mma.sync, 2 tcgen05
 std::atomic<int> g_decode_chunk{0};
 std::atomic<int> g_prefill_kernel{0};
 std::atomic<int> g_decode_early{0};
@@ -136,6 +137,7 @@ int run_prefill(const PrefillParams &p, bool bf16, cudaStream_t stream) {
     e = launch_attn_prefill_tc5(p, bf16, stream);
     if (e == cudaSuccess) {
       g_launches += 1;
+      g_last_prefill_kernel = 2;
       return GPU_OPS_OK;
     }
     if (e != cudaErrorNotSupported || which == 2) return cuda_fail(e, "tcgen05 prefill attention launch");
@@ -144,6 +146,7 @@ int run_prefill(const PrefillParams &p, bool bf16, cudaStream_t stream) {
   e = launch_attn_prefill_mma(p, bf16, stream);
   if (e != cudaSuccess) return cuda_fail(e, "prefill attention launch");
   g_launches += 1;
+  g_last_prefill_kernel = 1;
   return GPU_OPS_OK;
 }
 
@@ -179,6 +182,7 @@ int ref_attention(void *out, const void *q, const void *k, const void *v, int m,
     p.m = m;
     p.offset = offset;
     p.scale_log2 = scale_log2_of(head_dim);
+    p.error_flag = kernel_error_word_dev();
     // split only if the caller registered scratch for this device
     p.chunk = ((n + 63) / 64) * 64;
     p.max_splits = 1;
@@ -261,6 +265,7 @@ int ref_rope(void *out_q, void *out_k, const void *freqs, const void *in_q, cons
 
 namespace b200attn {
 void set_last_error(const char *msg) { g_last_error = msg ? msg : ""; }
+void add_launch_count(int launches) { g_launches += launches; }
 } // namespace b200attn
 
 namespace {
@@ -662,6 +667,7 @@ static int decode_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, v
   p.scale_log2 = scale_log2_of(desc->head_dim);
   p.pg = pg;
   p.early_kv = g_decode_early.load();
+  p.error_flag = kernel_error_word_dev();
   p.chunk = pick_chunk(desc->batch, desc->n_kv_heads, desc->total_kv_len, max_kv_len);
   p.max_splits = (max_kv_len + p.chunk - 1) / p.chunk;
   if (p.max_splits > 1) {
@@ -951,6 +957,8 @@ int gpu_attn_set_prefill_kernel(int which) {
   g_prefill_kernel.store(which);
   return GPU_OPS_OK;
 }
+
+int gpu_attn_last_prefill_kernel(void) { return g_last_prefill_kernel; }
 
 int gpu_ops_kernel_status(void) { return attn_tc5_error_status(); }
 

@@ -45,6 +45,68 @@ void InitFreqCIS(float *out, int head_dim, int max_seq_len, float theta, DataTyp
   }
 }
 
+// ---- cache layout and per-step state ------------------------------------------------
+size_t KVCacheLayout(gpu_attn_desc *desc, CacheLayout layout, int n_kv_heads, int max_seq_len, int head_dim) {
+  const long D = head_dim;
+  desc->cache_seq_stride = static_cast<long>(n_kv_heads) * max_seq_len * D;
+  if (layout == CacheLayout::HeadMajor) {
+    desc->cache_head_stride = static_cast<long>(max_seq_len) * D;
+    desc->cache_pos_stride = D;
+  } else {
+    desc->cache_head_stride = D;
+    desc->cache_pos_stride = n_kv_heads * D;
+  }
+  return static_cast<size_t>(desc->cache_seq_stride);
+}
+
+DecodeStep::~DecodeStep() {
+  for (int i = 0; i < 2; ++i) {
+    if (uploaded_[i]) cudaEventDestroy(uploaded_[i]);
+    if (pinned_[i]) cudaFreeHost(pinned_[i]);
+  }
+}
+
+bool DecodeStep::Init(int max_batch, int n_heads, int n_kv_heads, DataType dt) {
+  if (pinned_[0] || max_batch <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return false;
+  desc_ = gpu_attn_desc{};
+  desc_.dtype = static_cast<int32_t>(dt);
+  desc_.batch = max_batch;
+  desc_.n_heads = n_heads;
+  desc_.n_kv_heads = n_kv_heads;
+  desc_.head_dim = 128;
+  plan_bytes_ = gpu_attn_decode_plan_bytes(&desc_, 0);
+  if (!plan_bytes_) return false;
+  // scratch for the most pieces a plan can have: one per cache plus one per cut
+  const size_t max_slots = static_cast<size_t>(max_batch) * n_kv_heads + 1024;
+  workspace_bytes_ = max_slots * static_cast<size_t>(n_heads / n_kv_heads) * 129 * sizeof(float);
+  for (int i = 0; i < 2; ++i) {
+    if (cudaHostAlloc(&pinned_[i], plan_bytes_, cudaHostAllocDefault) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&uploaded_[i], cudaEventDisableTiming) != cudaSuccess) return false;
+  }
+  plan_dev_ = Tensor::MakeGPUTensor(plan_bytes_, DT_UINT8);
+  workspace_ = Tensor::MakeGPUTensor(workspace_bytes_, DT_UINT8);
+  return plan_dev_->data_ptr && workspace_->data_ptr;
+}
+
+int DecodeStep::Prepare(const int32_t *kv_len_host, int batch, bool append_new, cudaStream_t stream) {
+  if (!pinned_[0] || !kv_len_host || batch <= 0 || batch > desc_.batch) return GPU_OPS_E_INVALID;
+  const int slot = cur_ < 0 ? 0 : 1 - cur_;
+  // the buffer last served the step before the previous one: its upload has long been read
+  if (in_flight_[slot] && cudaEventSynchronize(uploaded_[slot]) != cudaSuccess) return GPU_OPS_E_CUDA;
+  gpu_attn_desc d = desc_;
+  d.batch = batch;
+  if (int rc = gpu_attn_decode_plan(&d, kv_len_host, append_new ? 1 : 0, 0, pinned_[slot], plan_bytes_)) return rc;
+  const size_t used = gpu_attn_decode_plan_size(pinned_[slot]);
+  if (gpu_attn_decode_plan_workspace_bytes(pinned_[slot]) > workspace_bytes_) return GPU_OPS_E_WORKSPACE;
+  if (cudaMemcpyAsync(plan_dev_->data_ptr, pinned_[slot], used, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaEventRecord(uploaded_[slot], stream) != cudaSuccess)
+    return GPU_OPS_E_CUDA;
+  in_flight_[slot] = true;
+  cur_ = slot;
+  batch_ = batch;
+  return GPU_OPS_OK;
+}
+
 // ---- layer -----------------------------------------------------------------------
 AttentionLayerGPUImpl::~AttentionLayerGPUImpl() { UnInit(); }
 
@@ -53,15 +115,14 @@ void AttentionLayerGPUImpl::UnInit() {
   v_cache.reset();
   freq_cis_owned_.reset();
   workspace_.reset();
-  kv_len_dev_.reset();
   staging_in_.reset();
   staging_out_.reset();
-  if (kv_len_pinned_) {
-    cudaFreeHost(kv_len_pinned_);
-    kv_len_pinned_ = nullptr;
-  }
+  staging_in_bytes_ = staging_out_bytes_ = 0;
+  own_step_.reset();
   k_cache_raw_ = v_cache_raw_ = nullptr;
   freq_cis_ = nullptr;
+  shared_lens_ = nullptr;
+  shared_step_ = nullptr;
 }
 
 bool AttentionLayerGPUImpl::Init(const AttentionConfig &cfg, const float *shared_freq_cis, void *k_cache_ext,
@@ -100,11 +161,7 @@ bool AttentionLayerGPUImpl::Init(const AttentionConfig &cfg, const float *shared
   gpu_attn_desc d = MakeDesc(cfg.max_batch, 1, 0, 0, 0, 0);
   workspace_bytes_ = gpu_attn_decode_workspace_bytes(&d, cfg.max_seq_len);
   workspace_ = Tensor::MakeGPUTensor(workspace_bytes_ > 0 ? workspace_bytes_ : 16, DT_UINT8);
-  kv_len_dev_ = Tensor::MakeGPUTensor(cfg.max_batch, DT_INT32);
-  if (cudaHostAlloc(reinterpret_cast<void **>(&kv_len_pinned_), sizeof(int32_t) * cfg.max_batch, cudaHostAllocDefault) !=
-      cudaSuccess)
-    return false;
-  return workspace_->data_ptr && kv_len_dev_->data_ptr;
+  return workspace_->data_ptr != nullptr;
 }
 
 gpu_attn_desc AttentionLayerGPUImpl::MakeDesc(int batch, int m, long q_tok, long q_seq, long kv_tok, long kv_seq) const {
@@ -122,30 +179,41 @@ gpu_attn_desc AttentionLayerGPUImpl::MakeDesc(int batch, int m, long q_tok, long
   d.kv_in_seq_stride = kv_seq ? kv_seq : m * d.kv_in_tok_stride;
   d.out_tok_stride = cfg_.n_heads * D;
   d.out_seq_stride = m * d.out_tok_stride;
-  d.cache_seq_stride = static_cast<long>(cfg_.n_kv_heads) * cfg_.max_seq_len * D;
-  if (cfg_.cache_layout == CacheLayout::HeadMajor) {
-    d.cache_head_stride = static_cast<long>(cfg_.max_seq_len) * D;
-    d.cache_pos_stride = D;
-  } else {
-    d.cache_head_stride = D;
-    d.cache_pos_stride = cfg_.n_kv_heads * D;
-  }
+  KVCacheLayout(&d, cfg_.cache_layout, cfg_.n_kv_heads, cfg_.max_seq_len, cfg_.head_dim);
   return d;
 }
 
-static long sum_lens(const int32_t *lens, int batch) {
-  long s = 0;
-  for (int b = 0; b < batch; ++b) s += lens[b] + 1;
-  return s;
-}
-
-int AttentionLayerGPUImpl::UploadLens(const int32_t *lens, int batch, cudaStream_t stream) {
-  // the pinned staging array is reused by every call: wait until the previous upload has been read
-  cudaError_t e = cudaStreamSynchronize(stream);
-  if (e != cudaSuccess) return GPU_OPS_E_CUDA;
-  std::memcpy(kv_len_pinned_, lens, sizeof(int32_t) * batch);
-  e = cudaMemcpyAsync(kv_len_dev_->data_ptr, kv_len_pinned_, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, stream);
-  return e == cudaSuccess ? GPU_OPS_OK : GPU_OPS_E_CUDA;
+int AttentionLayerGPUImpl::DecodeStepCall(gpu_attn_desc &d, void *out, const void *q, const void *k, const void *v,
+                                          const int32_t *kv_len_host, int uniform_len, int batch, cudaStream_t stream) {
+  const DecodeStep *step = shared_step_;
+  if (!step && shared_lens_) {
+    d.total_kv_len = shared_total_;
+    return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_, shared_lens_,
+                                 nullptr, 1, shared_max_len_, workspace_->data_ptr, workspace_bytes_, stream);
+  }
+  if (!step) {
+    // no state shared by the model: cut the work for this call
+    std::vector<int32_t> uniform;
+    if (!kv_len_host) {
+      uniform.assign(batch, uniform_len);
+      kv_len_host = uniform.data();
+    }
+    for (int b = 0; b < batch; ++b)
+      if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
+    if (!own_step_) {
+      own_step_.reset(new DecodeStep());
+      if (!own_step_->Init(cfg_.max_batch, cfg_.n_heads, cfg_.n_kv_heads, cfg_.data_type)) {
+        own_step_.reset();
+        return GPU_OPS_E_CUDA;
+      }
+    }
+    if (int rc = own_step_->Prepare(kv_len_host, batch, true, stream)) return rc;
+    step = own_step_.get();
+  }
+  if (!step->ready() || step->batch() != batch) return GPU_OPS_E_INVALID;
+  return gpu_attn_decode_planned_layer(&d, nullptr, step->plan_host(), step->plan_dev(), out, nullptr, nullptr, q, k, v,
+                                       k_cache_raw_, v_cache_raw_, freq_cis_, nullptr, step->workspace(),
+                                       step->workspace_bytes(), stream);
 }
 
 int AttentionLayerGPUImpl::ForwardRaw(void *out, const void *q, const void *k, const void *v, InferenceCtx &ctx,
@@ -176,25 +244,9 @@ int AttentionLayerGPUImpl::ForwardRaw(void *out, const void *q, const void *k, c
 int AttentionLayerGPUImpl::DecodeRagged(void *out, const void *q, const void *k, const void *v,
                                         const int32_t *kv_len_host, int batch, cudaStream_t stream) {
   if (batch <= 0 || batch > cfg_.max_batch) return GPU_OPS_E_INVALID;
-  if (shared_lens_) {
-    gpu_attn_desc d = MakeDesc(batch, 1, 0, 0, 0, 0);
-    d.total_kv_len = shared_total_;
-    return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_, shared_lens_,
-                                 nullptr, 1, shared_max_len_, workspace_->data_ptr, workspace_bytes_, stream);
-  }
-  if (!kv_len_host) return GPU_OPS_E_INVALID;
-  int max_len = 0;
-  for (int b = 0; b < batch; ++b) {
-    if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
-    if (kv_len_host[b] + 1 > max_len) max_len = kv_len_host[b] + 1;
-  }
-  int rc = UploadLens(kv_len_host, batch, stream);
-  if (rc) return rc;
+  if (!kv_len_host && !shared_step_ && !shared_lens_) return GPU_OPS_E_INVALID;
   gpu_attn_desc d = MakeDesc(batch, 1, 0, 0, 0, 0);
-  d.total_kv_len = sum_lens(kv_len_host, batch);
-  return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_,
-                               static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
-                               workspace_->data_ptr, workspace_bytes_, stream);
+  return DecodeStepCall(d, out, q, k, v, kv_len_host, 0, batch, stream);
 }
 
 std::shared_ptr<Tensor> AttentionLayerGPUImpl::Forward(std::shared_ptr<Tensor> q, std::shared_ptr<Tensor> k,
@@ -235,41 +287,27 @@ int AttentionLayerGPUImpl::ForwardFused(void *out, const void *qkv, const void *
   }
   const void *q = base, *k = base + cfg_.n_heads * D * 2, *v = base + (cfg_.n_heads + cfg_.n_kv_heads) * D * 2;
   gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
-  if (shared_lens_) {
-    d.total_kv_len = shared_total_;
-    return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_, shared_lens_,
-                                 nullptr, 1, shared_max_len_, workspace_->data_ptr, workspace_bytes_, s);
-  }
-  std::vector<int32_t> uniform;
-  if (!kv_len_host) {
-    uniform.assign(batch, ctx.prev_pos);
-    kv_len_host = uniform.data();
-  }
-  int max_len = 0;
-  for (int b = 0; b < batch; ++b) {
-    if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
-    if (kv_len_host[b] + 1 > max_len) max_len = kv_len_host[b] + 1;
-  }
-  if (int rc = UploadLens(kv_len_host, batch, s)) return rc;
-  d.total_kv_len = sum_lens(kv_len_host, batch);
-  return gpu_attn_decode_layer(&d, out, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_, freq_cis_,
-                               static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
-                               workspace_->data_ptr, workspace_bytes_, s);
+  return DecodeStepCall(d, out, q, k, v, kv_len_host, ctx.prev_pos, batch, s);
 }
 
 int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, InferenceCtx &ctx, int batch,
                                        const int32_t *kv_len_host) {
-  if (batch <= 0 || batch > cfg_.max_batch || ctx.cur_size <= 0) return GPU_OPS_E_INVALID;
+  if (batch <= 0 || batch > cfg_.max_batch || ctx.cur_size <= 0 || ctx.prev_pos < 0 || ctx.cur_pos > cfg_.max_seq_len)
+    return GPU_OPS_E_INVALID;
   const long D = cfg_.head_dim;
   const long row = (cfg_.n_heads + 2L * cfg_.n_kv_heads) * D;
   const size_t in_bytes = static_cast<size_t>(batch) * ctx.cur_size * row * 2;
   const size_t out_bytes = static_cast<size_t>(batch) * ctx.cur_size * cfg_.n_heads * D * 2;
   if (in_bytes > staging_in_bytes_) {
+    staging_in_bytes_ = 0;
     staging_in_ = Tensor::MakeGPUTensor(in_bytes, DT_UINT8);
+    if (!staging_in_ || !staging_in_->data_ptr) return GPU_OPS_E_CUDA;
     staging_in_bytes_ = in_bytes;
   }
   if (out_bytes > staging_out_bytes_) {
+    staging_out_bytes_ = 0;
     staging_out_ = Tensor::MakeGPUTensor(out_bytes, DT_UINT8);
+    if (!staging_out_ || !staging_out_->data_ptr) return GPU_OPS_E_CUDA;
     staging_out_bytes_ = out_bytes;
   }
   cudaStream_t s = ctx.gpu_stream;
@@ -278,30 +316,10 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
   const char *base = static_cast<const char *>(staging_in_->data_ptr);
   const void *q = base, *k = base + cfg_.n_heads * D * 2, *v = base + (cfg_.n_heads + cfg_.n_kv_heads) * D * 2;
   int rc;
-  if (ctx.cur_size == 1 && shared_lens_) {
-    gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
-    d.total_kv_len = shared_total_;
-    rc = gpu_attn_decode_layer(&d, staging_out_->data_ptr, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_,
-                               freq_cis_, shared_lens_, nullptr, 1, shared_max_len_, workspace_->data_ptr,
-                               workspace_bytes_, s);
-  } else if (ctx.cur_size == 1) {
-    std::vector<int32_t> uniform;
-    if (!kv_len_host) {
-      uniform.assign(batch, ctx.prev_pos);
-      kv_len_host = uniform.data();
-    }
-    int max_len = 0;
-    for (int b = 0; b < batch; ++b) {
-      if (kv_len_host[b] < 0 || kv_len_host[b] + 1 > cfg_.max_seq_len) return GPU_OPS_E_INVALID;
-      if (kv_len_host[b] + 1 > max_len) max_len = kv_len_host[b] + 1;
-    }
-    if ((rc = UploadLens(kv_len_host, batch, s))) return rc;
+  if (ctx.cur_size == 1) {
     // q, k, v are columns of one packed row: strides say so
     gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
-    d.total_kv_len = sum_lens(kv_len_host, batch);
-    rc = gpu_attn_decode_layer(&d, staging_out_->data_ptr, nullptr, nullptr, q, k, v, k_cache_raw_, v_cache_raw_,
-                               freq_cis_, static_cast<const int32_t *>(kv_len_dev_->data_ptr), nullptr, 1, max_len,
-                               workspace_->data_ptr, workspace_bytes_, s);
+    rc = DecodeStepCall(d, staging_out_->data_ptr, q, k, v, kv_len_host, ctx.prev_pos, batch, s);
   } else {
     gpu_attn_desc d = MakeDesc(batch, ctx.cur_size, row, ctx.cur_size * row, row, ctx.cur_size * row);
     // rotate Q in place inside the staging buffer

@@ -40,6 +40,43 @@ void InitFreqCIS(float *out, int head_dim, int max_seq_len, float theta, DataTyp
 
 enum class CacheLayout { TokenMajor = 0, HeadMajor = 1 };
 
+// The three cache strides of gpu_attn_desc for a per-layer KV cache of `max_seq_len` positions per
+// sequence: token-major [seq][pos][kv_head][D] is the reference's layout
+// (src/llama2_layer_npu.cpp:1148-1149: kvH * D * max_seq_len elements, appended at byte offset
+// prev_pos * kvH * D * 2, :830-843), head-major [seq][kv_head][pos][D] keeps one head's positions
+// contiguous.  Returns the elements one sequence occupies.
+size_t KVCacheLayout(gpu_attn_desc *desc, CacheLayout layout, int n_kv_heads, int max_seq_len, int head_dim);
+
+// What a model prepares once per decode step for all its layers: the work partition of the step
+// (gpu_attn_decode_plan) for the sequences' cache lengths, which the host knows as the reference's
+// generation loop knows cur_pos / prev_pos (src/model_base.hpp:40-48), its device copy and the
+// scratch of the planned decode kernel.  Prepare() never waits for the stream: the plan is built
+// in one of two pinned buffers used by alternate steps (an event tells when a buffer's upload has
+// been read) and the device copy is overwritten in stream order, behind the previous step's kernels.
+class DecodeStep {
+public:
+  ~DecodeStep();
+  bool Init(int max_batch, int n_heads, int n_kv_heads, DataType dt);
+  // kv_len_host: tokens already cached per sequence.  Enqueues the upload on `stream`; the layers'
+  // calls of this step must follow on the same stream.
+  int Prepare(const int32_t *kv_len_host, int batch, bool append_new, cudaStream_t stream);
+  bool ready() const { return cur_ >= 0; }
+  int batch() const { return batch_; }
+  const void *plan_host() const { return cur_ >= 0 ? pinned_[cur_] : nullptr; }
+  const void *plan_dev() const { return plan_dev_ ? plan_dev_->data_ptr : nullptr; }
+  void *workspace() const { return workspace_ ? workspace_->data_ptr : nullptr; }
+  size_t workspace_bytes() const { return workspace_bytes_; }
+
+private:
+  gpu_attn_desc desc_{};
+  size_t plan_bytes_{0}, workspace_bytes_{0};
+  void *pinned_[2] = {nullptr, nullptr};
+  cudaEvent_t uploaded_[2] = {nullptr, nullptr};
+  bool in_flight_[2] = {false, false};
+  int cur_{-1}, batch_{0};
+  std::shared_ptr<Tensor> plan_dev_, workspace_;
+};
+
 struct AttentionConfig {
   int n_heads{0};
   int n_kv_heads{0};
@@ -102,6 +139,9 @@ public:
     shared_max_len_ = max_kv_len;
     shared_total_ = total_kv_len;
   }
+  // The step state the model prepared for all its layers (DecodeStep::Prepare): while set, decode
+  // calls run the planned kernel on it and ignore their own length arguments.  NULL unsets.
+  void SetSharedStep(const DecodeStep *step) { shared_step_ = step; }
 
   const AttentionConfig &config() const { return cfg_; }
   void *k_cache_ptr() const { return k_cache_raw_; }
@@ -112,7 +152,10 @@ public:
 
 protected:
   gpu_attn_desc MakeDesc(int batch, int m, long q_tok, long q_seq, long kv_tok, long kv_seq) const;
-  int UploadLens(const int32_t *lens, int batch, cudaStream_t stream);
+  // One decode step for q / k / v addressed by `d`: on the shared step state, on the shared device
+  // lengths, or on a plan built here from kv_len_host (NULL: every sequence holds uniform_len tokens).
+  int DecodeStepCall(gpu_attn_desc &d, void *out, const void *q, const void *k, const void *v,
+                     const int32_t *kv_len_host, int uniform_len, int batch, cudaStream_t stream);
 
   AttentionConfig cfg_;
   void *k_cache_raw_{nullptr};
@@ -121,13 +164,13 @@ protected:
   const float *freq_cis_{nullptr};
   std::shared_ptr<Tensor> workspace_;
   size_t workspace_bytes_{0};
-  std::shared_ptr<Tensor> kv_len_dev_;
-  int32_t *kv_len_pinned_{nullptr};
+  std::unique_ptr<DecodeStep> own_step_; // for calls that come with host lengths and no shared step
   std::shared_ptr<Tensor> staging_in_, staging_out_; // device side of ForwardHost
   size_t staging_in_bytes_{0}, staging_out_bytes_{0};
   const int32_t *shared_lens_{nullptr};
   int shared_max_len_{0};
   long shared_total_{0};
+  const DecodeStep *shared_step_{nullptr};
 };
 
 // Llama-2 flavour: MHA, fp16 (the reference forces DT_FLOAT16 for llama2,

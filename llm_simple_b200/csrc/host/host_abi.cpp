@@ -86,6 +86,34 @@ int gpu_attention_layer_set_shared_lens(void *layer, const int32_t *kv_len_dev, 
   return GPU_OPS_OK;
 }
 
+void *gpu_decode_step_create(int max_batch, int n_heads, int n_kv_heads, int dt) {
+  DecodeStep *step = new DecodeStep();
+  if (!step->Init(max_batch, n_heads, n_kv_heads, static_cast<DataType>(dt))) {
+    delete step;
+    return nullptr;
+  }
+  return step;
+}
+
+void gpu_decode_step_destroy(void *step) { delete static_cast<DecodeStep *>(step); }
+
+int gpu_decode_step_prepare(void *step, const int32_t *kv_len_host, int batch, int append_new, gpu_stream_t stream) {
+  if (!step) return GPU_OPS_E_INVALID;
+  return static_cast<DecodeStep *>(step)->Prepare(kv_len_host, batch, append_new != 0, static_cast<cudaStream_t>(stream));
+}
+
+int gpu_attention_layer_set_shared_step(void *layer, void *step) {
+  if (!layer) return GPU_OPS_E_INVALID;
+  as_layer(layer)->SetSharedStep(static_cast<DecodeStep *>(step));
+  return GPU_OPS_OK;
+}
+
+size_t gpu_kv_cache_layout(gpu_attn_desc *desc, int cache_layout, int n_kv_heads, int max_seq_len, int head_dim) {
+  if (!desc || n_kv_heads <= 0 || max_seq_len <= 0 || head_dim <= 0 || (cache_layout != 0 && cache_layout != 1)) return 0;
+  return KVCacheLayout(desc, cache_layout == 0 ? CacheLayout::TokenMajor : CacheLayout::HeadMajor, n_kv_heads, max_seq_len,
+                       head_dim);
+}
+
 int gpu_attention_layer_forward_host(void *layer, void *out_host, const void *qkv_host, int batch, int cur_pos,
                                      int prev_pos, const int32_t *kv_len_host, gpu_stream_t stream) {
   if (!layer || !out_host || !qkv_host || cur_pos < prev_pos || prev_pos < 0) return GPU_OPS_E_INVALID;

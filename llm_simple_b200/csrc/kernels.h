@@ -9,6 +9,8 @@ namespace b200attn {
 
 // Record the message gpu_ops_last_error_string() returns on the calling thread.
 void set_last_error(const char *msg);
+// Add to the calling thread's gpu_ops_launch_count().
+void add_launch_count(int launches);
 
 // ---- paged KV cache --------------------------------------------------------
 // Optional indirection of cache positions: with table != nullptr, position pos of
@@ -87,7 +89,12 @@ struct DecodeParams {
   KvPaging pg;
   int early_kv;         // 1: fetch the first K/V tiles before waiting for the preceding kernels
   int no_merge;         // 1: leave the split partials in (ws_o, ws_lse); the caller merges them
+  int *error_flag;      // status word (host-mapped), or NULL
 };
+
+// Status codes the kernels store in the host-visible status word (besides the codes of waits that
+// gave up): a sequence was longer than the bound the launch was sized for.
+constexpr int kStatusLengthBeyondBound = 40;
 
 cudaError_t launch_attn_decode(const DecodeParams &p, bool bf16, cudaStream_t stream, int *launches);
 
@@ -205,6 +212,14 @@ cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStrea
 // tcgen05 / TMEM / TMA kernel; same contract.  Returns cudaErrorNotSupported if
 // the geometry cannot be described by its tensor maps.
 cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream);
+// Tensor maps are pure functions of (base, geometry): a small per-thread cache of the most recent
+// ones saves the driver call on repeated launches (a layer calls with the same buffers every step).
+struct TensorMapKey {
+  const void *base;
+  uint64_t n1, n2, n3;
+  long s1, s2, s3;
+  uint32_t box1, box2, bf16, pad; // no padding bytes: compared with memcmp
+};
 // Non-zero once a bounded wait inside a kernel on the current device has given up.
 int attn_tc5_error_status();
 void attn_clear_error_status();

@@ -68,7 +68,7 @@ template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_ker
     // ---- this rank's splits of the row -> one partial (the arithmetic of attn_merge_kernel)
     const int b = row / p.rows_per_seq;
     const int total = p.kv_len_dev[b] + p.append;
-    const int n_parts = max(1, (total + p.chunk - 1) / p.chunk);
+    const int n_parts = min(max(1, (total + p.chunk - 1) / p.chunk), p.max_splits); // never beyond the row's slots
     float M = -INFINITY;
     for (int i = 0; i < n_parts; ++i) M = fmaxf(M, p.ws_lse[static_cast<long>(row) * p.max_splits + i]);
     float W = 0.f, o = 0.f;

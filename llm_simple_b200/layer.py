@@ -13,6 +13,8 @@ EXPORTS = [
     "gpu_attention_layer_create", "gpu_attention_layer_destroy", "gpu_attention_layer_forward",
     "gpu_attention_layer_decode_ragged", "gpu_attention_layer_set_shared_lens",
     "gpu_attention_layer_forward_host", "gpu_attention_layer_forward_fused", "gpu_attention_layer_cache",
+    "gpu_decode_step_create", "gpu_decode_step_destroy", "gpu_decode_step_prepare",
+    "gpu_attention_layer_set_shared_step", "gpu_kv_cache_layout",
 ]
 
 LLAMA2, QWEN2 = 0, 1
@@ -41,6 +43,13 @@ def lib():
         L.gpu_attention_layer_forward_host.argtypes = [vp, vp, vp, i, i, i, vp, vp]
         L.gpu_attention_layer_forward_fused.argtypes = [vp, vp, vp, vp, i, i, i, vp, vp]
         L.gpu_attention_layer_cache.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
+        L.gpu_decode_step_create.restype = vp
+        L.gpu_decode_step_create.argtypes = [i, i, i, i]
+        L.gpu_decode_step_destroy.argtypes = [vp]
+        L.gpu_decode_step_prepare.argtypes = [vp, vp, i, i, vp]
+        L.gpu_attention_layer_set_shared_step.argtypes = [vp, vp]
+        L.gpu_kv_cache_layout.restype = sz
+        L.gpu_kv_cache_layout.argtypes = [ctypes.POINTER(ops.AttnDesc), i, i, i, i]
         _ready = True
     return L
 
@@ -56,6 +65,37 @@ def init_freq_cis(head_dim, max_seq_len, theta, dt):
     out = np.empty((max_seq_len, head_dim // 2, 2), dtype=np.float32)
     lib().gpu_init_freq_cis(out.ctypes.data, head_dim, max_seq_len, theta, dt)
     return out
+
+
+def kv_cache_layout(desc, cache_layout, n_kv_heads, max_seq_len, head_dim=128):
+    """Fills desc's three cache strides for the layout; returns the elements per sequence."""
+    return int(lib().gpu_kv_cache_layout(ctypes.byref(desc), cache_layout, n_kv_heads, max_seq_len, head_dim))
+
+
+class DecodeStep:
+    """Per-step state a model shares between its layers: the work partition of the decode
+    step for the sequences' cache lengths, uploaded once (gpu_decode_step_*)."""
+
+    def __init__(self, max_batch, n_heads, n_kv_heads, dt):
+        self.h = lib().gpu_decode_step_create(max_batch, n_heads, n_kv_heads, dt)
+        if not self.h:
+            raise ops.GpuOpsError("gpu_decode_step_create failed")
+
+    def prepare(self, kv_len, append_new=True, stream=None):
+        lens = np.ascontiguousarray(kv_len, dtype=np.int32)
+        ops._check(lib().gpu_decode_step_prepare(self.h, lens.ctypes.data, len(lens), int(bool(append_new)),
+                                                 ops._stream(stream)))
+
+    def close(self):
+        if self.h:
+            lib().gpu_decode_step_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class AttentionLayer:
@@ -95,6 +135,11 @@ class AttentionLayer:
     def set_shared_lens(self, kv_len_dev, max_kv_len, total_kv_len=0):
         ops._check(lib().gpu_attention_layer_set_shared_lens(self.h, ops._ptr(kv_len_dev), max_kv_len,
                                                              total_kv_len))
+
+    def set_shared_step(self, step):
+        """step: a DecodeStep prepared for this decode step, or None."""
+        self._step = step
+        ops._check(lib().gpu_attention_layer_set_shared_step(self.h, step.h if step is not None else None))
 
     def forward_host(self, out_host, qkv_host, batch, cur_pos, prev_pos, kv_len=None, stream=None):
         lens_ptr = None

@@ -21,13 +21,13 @@ EXPORTS = [
     "gpu_flash_attn_layer", "gpu_flash_attn_gqa_layer", "gpu_flash_attn_opt_prefill_layer",
     "gpu_rope_layer", "gpu_rope_single_layer", "gpu_split_qkv_layer", "gpu_rope_kv_append_layer",
     "gpu_qkv_rope_kv_append_layer", "gpu_bias_add_layer", "gpu_attn_prefill_layer",
-    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_plan_bytes", "gpu_attn_decode_plan",
+    "gpu_attn_decode_layer", "gpu_attn_decode_layer_noalloc", "gpu_attn_decode_noalloc_prepare", "gpu_attn_decode_plan_bytes", "gpu_attn_decode_plan",
     "gpu_attn_decode_plan_size", "gpu_attn_decode_plan_workspace_bytes", "gpu_attn_decode_planned_layer", "gpu_rope_kv_append_paged_layer",
     "gpu_attn_decode_paged_layer", "gpu_attn_prefill_paged_layer", "gpu_attn_decode_workspace_bytes", "gpu_attn_merge_lse_layer", "gpu_attn_merge_packed_layer",
     "gpu_attn_xchg_buffer_bytes", "gpu_attn_xchg_local_slot", "gpu_attn_xchg_merge_layer",
     "gpu_attn_decode_xchg_layer",
     "gpu_peer_buffer_alloc", "gpu_peer_buffer_open", "gpu_peer_buffer_close", "gpu_peer_buffer_free",
-    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel",
+    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel", "gpu_attn_last_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status", "gpu_ops_clear_kernel_status",
 ]
 
@@ -323,11 +323,17 @@ def gpu_attn_decode_planned_layer(desc, pages, plan, out, o_partial, lse_partial
                                                workspace_bytes, _stream(stream)))
 
 
+def gpu_attn_decode_noalloc_prepare():
+    """Resolves the built-in scratch on the current device (takes its 16 MiB): call at start-up."""
+    _check(lib().gpu_attn_decode_noalloc_prepare())
+
+
 def gpu_attn_decode_layer_noalloc(desc, out, q_in, k_in, v_in, k_cache, v_cache, freqs_cis, kv_len_dev,
                                   rope_pos_dev, append_new, max_kv_len, stream=None):
     """The fused decode step with the library's built-in 16 MiB scratch: for callers
-    that cannot allocate device memory.  Make the first call on a device outside any
-    stream capture; do not overlap calls on one device."""
+    that cannot allocate device memory.  Resolve the scratch at start-up
+    (gpu_attn_decode_noalloc_prepare) before the host reserves the device memory and
+    outside any stream capture; do not overlap calls on one device."""
     _check(lib().gpu_attn_decode_layer_noalloc(ctypes.byref(desc), _ptr(out), _ptr(q_in), _ptr(k_in),
                                                _ptr(v_in), _ptr(k_cache), _ptr(v_cache), _ptr(freqs_cis),
                                                _ptr(kv_len_dev), _ptr(rope_pos_dev), int(bool(append_new)),
@@ -403,6 +409,10 @@ def gpu_attn_set_decode_chunk(positions):
 
 def gpu_attn_set_prefill_kernel(which):
     _check(lib().gpu_attn_set_prefill_kernel(which))
+
+
+def gpu_attn_last_prefill_kernel():
+    return int(lib().gpu_attn_last_prefill_kernel())
 
 
 def gpu_ops_clear_kernel_status():

@@ -72,3 +72,37 @@ def test_init_freq_cis_is_bit_identical_to_the_oracle(theta, dt):
     got = layer.init_freq_cis(128, 4100, theta, dt)
     want = orc.init_freq_cis(128, 4100, theta, dt)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_layer_rejects_positions_beyond_its_cache_before_any_launch(pool):
+    """Every forward entry point checks prev_pos / cur_pos against the cache the layer was
+    created for on the host, before a copy or a kernel is enqueued: a prefill that would append
+    beyond the cache must not reach the device (the kernels carry no cache extent)."""
+    table = np.zeros((64, 64, 2), dtype=np.float32)
+    lay = pool.AttentionLayer(pool.QWEN2, 4, 2, 64, 2, orc.DT_BFLOAT16, 1e6, True, shared_freq_cis=table.ctypes.data)
+    try:
+        L = pool.lib()
+        buf = np.zeros(1 << 20, dtype=np.uint8)
+        p = buf.ctypes.data
+        # cur_pos 65 > max_seq_len 64: prefill of 65 tokens, and a decode step at position 64
+        for cur_pos, prev_pos in ((65, 0), (65, 64)):
+            assert L.gpu_attention_layer_forward_host(lay.h, p, p, 1, cur_pos, prev_pos, None, None) == -1
+            assert L.gpu_attention_layer_forward(lay.h, p, p, p, p, 1, cur_pos, prev_pos, None) == -1
+            assert L.gpu_attention_layer_forward_fused(lay.h, p, p, None, 1, cur_pos, prev_pos, None, None) == -1
+        # batch beyond max_batch, negative start
+        assert L.gpu_attention_layer_forward_host(lay.h, p, p, 3, 8, 0, None, None) == -1
+        assert L.gpu_attention_layer_forward_host(lay.h, p, p, 1, 8, -1, None, None) == -1
+    finally:
+        lay.close()
+
+
+def test_kv_cache_layout_helper():
+    from llm_simple_b200 import layer, ops
+    d = ops.AttnDesc()
+    assert layer.kv_cache_layout(d, layer.TOKEN_MAJOR, 8, 4096) == 8 * 4096 * 128
+    assert (d.cache_seq_stride, d.cache_head_stride, d.cache_pos_stride) == (8 * 4096 * 128, 128, 8 * 128)
+    assert layer.kv_cache_layout(d, layer.HEAD_MAJOR, 8, 4096) == 8 * 4096 * 128
+    assert (d.cache_seq_stride, d.cache_head_stride, d.cache_pos_stride) == (8 * 4096 * 128, 4096 * 128, 128)
+    ref = ops.make_desc(ops.DT_BFLOAT16, 1, 40, 8, 1, 4096, layout="head")
+    assert (ref.cache_head_stride, ref.cache_pos_stride) == (d.cache_head_stride, d.cache_pos_stride)
+    assert layer.kv_cache_layout(d, 2, 8, 4096) == 0

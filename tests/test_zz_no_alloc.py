@@ -8,9 +8,13 @@ workspace.  Its split-KV scratch is a fixed 16 MiB array inside the library.
 
 Checked here through the C ABI: two calls in a row (the second with different,
 shorter caches, so that anything the first call left in the shared scratch
-would show) give the same result as the ordinary entry point with a caller
-workspace, within the tolerance of the other attention tests; a call that would
-need more than the built-in scratch is rejected before anything is launched.
+would show) give the same BITS as the ordinary entry point with a caller
+workspace and the same split size -- the two run the same kernels, so a
+tolerance would only hide a stale partial that slipped into a merge -- and
+agree with the CPU oracle within the tolerance of the other attention tests;
+fp16 and a call short enough to need no scratch at all are covered as well; a
+call that would need more than the built-in scratch is rejected before anything
+is launched.
 
 This file is named so that pytest collects it last: a run that stops at the
 first failure has then already run every other test.
@@ -20,7 +24,7 @@ import pytest
 import torch
 
 from oracle import oracle as orc
-from tests.gpu_util import BF16, D, MAX_ABS, MEAN_ABS, dev, host, rnd_bits
+from tests.gpu_util import BF16, D, FP16, TORCH_DT, assert_parity, dev, host, rnd_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -34,11 +38,12 @@ def _one_step(ops, lens, seed, use_noalloc, H=40, kvh=8, dt=BF16):
     v_new = dev(rnd_bits((batch, kvh * D), dt, seed + 2), dt)
     g = torch.Generator(device="cuda")
     g.manual_seed(seed)
-    kc = torch.empty((batch, kvh, max_pos, D), dtype=torch.bfloat16, device="cuda").normal_(generator=g)
-    vc = torch.empty((batch, kvh, max_pos, D), dtype=torch.bfloat16, device="cuda").normal_(generator=g)
+    kc = torch.empty((batch, kvh, max_pos, D), dtype=TORCH_DT[dt], device="cuda").normal_(generator=g)
+    vc = torch.empty((batch, kvh, max_pos, D), dtype=TORCH_DT[dt], device="cuda").normal_(generator=g)
+    kc0, vc0 = host(kc), host(vc)
     desc = ops.make_desc(dt, batch, H, kvh, 1, max_pos, layout="head", is_neox=True)
     lens_d = torch.tensor(lens, dtype=torch.int32, device="cuda")
-    out = torch.zeros((batch, H * D), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros((batch, H * D), dtype=TORCH_DT[dt], device="cuda")
     max_kv = max(lens) + 1
     if use_noalloc:
         ops.gpu_attn_decode_layer_noalloc(desc, out, q, k_new, v_new, kc, vc, table, lens_d, None, True, max_kv)
@@ -52,24 +57,44 @@ def _one_step(ops, lens, seed, use_noalloc, H=40, kvh=8, dt=BF16):
         finally:
             ops.gpu_attn_set_decode_chunk(0)
     torch.cuda.synchronize()
-    return orc.to_f32(host(out), dt), host(kc), host(vc)
+    inputs = (host(q), host(k_new), host(v_new), kc0, vc0, orc.init_freq_cis(D, max_pos, 1e6, dt))
+    return host(out), host(kc), host(vc), inputs
 
 
-def test_noalloc_entry_point_matches_the_workspace_entry_point_twice_in_a_row():
+def _oracle_step(inputs, lens, H, kvh, dt):
+    """The step on the CPU, sequence by sequence: rope -> append -> attention (fp32 golden)."""
+    q, k_new, v_new, kc, vc, table = inputs
+    outs = []
+    for b, L in enumerate(lens):
+        kc_tok = np.ascontiguousarray(kc[b, :, :L + 1].transpose(1, 0, 2)).reshape(L + 1, kvh * D)
+        vc_tok = np.ascontiguousarray(vc[b, :, :L + 1].transpose(1, 0, 2)).reshape(L + 1, kvh * D)
+        q_r = orc.rope_single_layer(q[b:b + 1], table, L, H, True, dt)
+        k_r = orc.rope_single_layer(k_new[b:b + 1], table, L, kvh, True, dt)
+        orc.kv_append(kc_tok, vc_tok, k_r, v_new[b:b + 1], L, kvh, D)
+        outs.append(orc.attn(q_r, kc_tok, vc_tok, 1, L + 1, L, H // kvh, kvh, D, dt, orc.MODE_GOLDEN, threads=8)[0])
+    return np.stack(outs)
+
+
+@pytest.mark.parametrize("dt", [BF16, FP16])
+def test_noalloc_entry_point_matches_the_workspace_entry_point_twice_in_a_row(dt):
     from llm_simple_b200 import ops
     ops.lib()
+    ops.gpu_attn_decode_noalloc_prepare()
+    H, kvh = 40, 8
     calls = [
         ([4096, 1024, 2500, 3333, 4000, 1500, 2047, 4095], 31),  # up to 9 splits per sequence
         ([700, 64, 1, 0, 1300], 47),                              # shorter: fewer splits than the scratch still holds
+        ([511, 300, 17], 53),                                     # one split: the scratch is not used at all
     ]
     for lens, seed in calls:
-        got, got_k, got_v = _one_step(ops, lens, seed, use_noalloc=True)
-        want, want_k, want_v = _one_step(ops, lens, seed, use_noalloc=False)
-        diff = np.abs(got - want)
-        assert np.all(np.isfinite(got))
-        assert diff.max() <= MAX_ABS and diff.mean() <= MEAN_ABS, (diff.max(), diff.mean())
-        # both entry points appended the same rotated K and raw V
+        ops.gpu_ops_launch_count(True)
+        got, got_k, got_v, inputs = _one_step(ops, lens, seed, True, H, kvh, dt)
+        assert ops.gpu_ops_launch_count(True) == (2 if max(lens) + 1 > 512 else 1)   # split kernel (+ merge)
+        want, want_k, want_v, _ = _one_step(ops, lens, seed, False, H, kvh, dt)
+        # same kernels, same split size: the same bits, output and appended K / V rows alike
+        assert np.array_equal(got, want)
         assert np.array_equal(got_k, want_k) and np.array_equal(got_v, want_v)
+        assert_parity(got, _oracle_step(inputs, lens, H, kvh, dt), dt, "no-alloc decode vs oracle")
 
 
 def test_noalloc_entry_point_rejects_what_its_scratch_cannot_hold():
