@@ -2,7 +2,7 @@
  * attn_oracle.cpp -- CPU restatement of llm_simple's attention hot path.
  *
  * TEST INFRASTRUCTURE ONLY (checker and timed CPU baseline); the shipped
- * library never calls it.  PARITY UNPINNED: see attn_oracle.h.
+ * library never calls it.  What pins it to reference code: see attn_oracle.h.
  *
  * The reference's CPU layer (src/llama2_layer_cpu.cpp) materialises, per call,
  * the full [H, m, n] score tensor three times (fp32, fp16, softmax fp16) and
@@ -212,6 +212,13 @@ void cpu_init_freq_cis_test(float *freq_cis, int head_dim, int max_seq_len) {
       freq_cis[2 * i + 1] = std::sin(angle);
     }
   }
+}
+
+/* the tensor rounding above on one raw fp32 pattern (for exhaustive comparison with util.cpp's routine) */
+uint16_t cpu_f32_bits_to_bf16(uint32_t fp32_bits) {
+  float f;
+  std::memcpy(&f, &fp32_bits, 4);
+  return f32_to_bf16_bits(f);
 }
 
 void cpu_f32_to_dt(uint16_t *dst, const float *src, size_t n, int dt) {

@@ -5,13 +5,24 @@
  * calls this; it exists so the CUDA kernels can be checked ("call both,
  * compare") and so a CPU baseline can be timed beside them.
  *
- * PARITY UNPINNED: the reference stores no golden vectors (its tests draw
- * unseeded random inputs and compute an Eigen golden at run time), its device
- * library is a closed AArch64/Ascend binary and its CPU layer needs Eigen,
- * boost and spdlog, none of which exist in this build environment.  The
- * restatement below is therefore pinned only by (a) analytic known-answer
- * cases and (b) an independently written numpy restatement of the reference
- * tests' golden math, whose outputs are stored as fixtures.
+ * HOW IT IS PINNED.  The reference stores no golden vectors (its tests draw
+ * unseeded random inputs and compute an Eigen golden at run time) and its
+ * device library is a closed AArch64/Ascend binary, so the pins are outputs of
+ * reference code compiled where it lies (oracle/build_ref.py ->
+ * oracle/_ref/libref_pins.so; fixtures tests/golden/ref_pins.npz made by
+ * tests/golden/make_ref_pins.py, checked by tests/test_ref_pins.py):
+ *   - fp32_to_bfloat16 (src/util.cpp:33-72): identical on all 2^32 patterns;
+ *   - the RoPE table of ModelBase::InitFreqCIS (src/model_base.cpp:27-83) and
+ *     of the tests' twin (tests/npu_op_test_util.cpp:109-142): bit-identical;
+ *   - the RoPE golden loop (tests/rope_single_layer_test.cpp:78-95), the mask
+ *     loop (tests/flash_attn_test.cpp:124-132), all_close
+ *     (tests/npu_op_test_util.cpp:33-48): bit-identical / same verdicts.
+ * NOT pinned by reference code: the two contractions and the softmax of the
+ * attention golden (Eigen tensor expressions; Eigen is not installed, so they
+ * cannot be compiled here).  Those are pinned by analytic known-answer cases,
+ * by an independently written numpy restatement and by PyTorch's CPU
+ * scaled_dot_product_attention in fp32 as a second opinion (<= 2e-5).  GQA head
+ * mapping, bf16 attention and batch > 1 have no reference test at all.
  *
  * Reference lines each function follows are cited at its definition.
  *
@@ -41,6 +52,10 @@ void cpu_init_freq_cis_test(float *freq_cis, int head_dim, int max_seq_len);
 
 /* src/util.cpp:33-72 */
 uint16_t cpu_fp32_to_bfloat16(uint32_t fp32_bits);
+
+/* round-to-nearest-even of one raw fp32 pattern to bf16 as the element conversions below do it
+ * (NaN stays NaN, which src/util.cpp's routine does not guarantee) */
+uint16_t cpu_f32_bits_to_bf16(uint32_t fp32_bits);
 
 /* element conversions used by the tests to prepare/inspect 16-bit buffers */
 void cpu_f32_to_dt(uint16_t *dst, const float *src, size_t n, int dt);

@@ -2,8 +2,8 @@
 
 Test infrastructure only: imported by tests/, by the smoke check and by the
 CPU-baseline leg of the benchmark.  The shipped package never imports it.
-PARITY UNPINNED (see attn_oracle.h): the reference stores no golden vectors and
-cannot run in this environment.
+What pins it to reference code (tests/test_ref_pins.py) and what stays pinned
+only by restatement (the attention contractions) is listed in attn_oracle.h.
 
 All 16-bit tensors travel as numpy uint16 arrays holding the raw fp16 / bf16
 bits; dtype codes are the reference's DataType values (prebuild/defs.hpp:8-18).

@@ -32,10 +32,16 @@ def run(binary, *args):
     ("--m", 1, "--n", 700, "--offset", 699, "--head_num", 32),                       # decode shape
     ("--m", 300, "--n", 812, "--offset", 512, "--head_num", 4, "--mode", "strict"),
     ("--m", 200, "--n", 200, "--group_size", 5, "--kv_head_num", 2, "--dtype", "bfloat16"),
+    (),                                                                             # the reference's defaults: m = n = 2048, 32 heads
+    ("--m", 4096, "--n", 8192, "--offset", 4096, "--head_num", 4),                  # a 4096-token chunk behind 4096 cached tokens
+    ("--m", 4096, "--n", 8192, "--offset", 4096, "--group_size", 5, "--kv_head_num", 1, "--dtype", "bfloat16"),
 ])
 def test_flash_attn_main(binaries, args):
     out = run(os.path.join(binaries, "flash_attn_main"), *args)
-    assert "within(1e-2,1e-3)" in out
+    assert "beyond: 0)" in out
+    if "bfloat16" not in args:        # fp16: no element needs the one-ulp term, and the reference's own verdict holds
+        assert out.count("within(1e-2,1e-3) yes") == 2 and "above 1e-2: 0 of" in out
+        assert "reference all_close(1e-3, 1e-3) on the fp32 golden: yes" in out
 
 
 @pytest.mark.parametrize("args", [
