@@ -409,11 +409,15 @@ int gpu_attn_set_decode_chunk(int positions);
 
 /* Which kernel gpu_attn_prefill_layer and the reference-shaped operators use
  * for rows beyond the small-m path: 0 = automatic, 1 = mma.sync kernel,
- * 2 = tcgen05 kernel.  Process-wide; for tests and measurements. */
+ * 2 = tcgen05 kernel, one CTA per 256 query rows, 3 = tcgen05 kernel in
+ * persistent form (one CTA per SM that takes work items from a counter, output
+ * through a TMA tensor store; same bits as 2, measured slower, opt-in only; not
+ * on a capturing stream).  Automatic = 2, else 1 where the tensor maps cannot
+ * describe the geometry.  Process-wide; for tests and measurements. */
 int gpu_attn_set_prefill_kernel(int which);
 
 /* Which kernel served the calling thread's last prefill-shaped call: 1 = mma.sync
- * kernel, 2 = tcgen05 kernel, 0 = none yet.  The automatic choice falls back to
+ * kernel, 2 = tcgen05 kernel, 3 = persistent tcgen05 kernel, 0 = none yet.  The automatic choice falls back to
  * the mma.sync kernel when the tcgen05 kernel's tensor maps cannot describe a
  * geometry (a stride that is no multiple of 16 bytes, pages below 128
  * positions); a caller that counts on the faster kernel can check here. */

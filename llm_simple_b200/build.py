@@ -16,7 +16,7 @@ LIB = os.path.join(HERE, "libgpu_ops.so")
 OBJ = os.path.join(HERE, "csrc", "_obj")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-CUDA_SOURCES = ["rope_append.cu", "attn_mma.cu", "attn_tc5.cu", "gpu_ops.cu", "decode_noalloc.cu", "xchg_merge.cu",
+CUDA_SOURCES = ["rope_append.cu", "attn_mma.cu", "attn_tc5.cu", "attn_tc5p.cu", "gpu_ops.cu", "decode_noalloc.cu", "xchg_merge.cu",
                 "attn_decode_tma.cu"]
 CXX_SOURCES = ["decode_plan.cpp", "host/device_gpu.cpp", "host/attention_layer_gpu.cpp", "host/host_abi.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -20,7 +20,7 @@ namespace {
 
 thread_local std::string g_last_error;
 thread_local long g_launches = 0;
-thread_local int g_last_prefill_kernel = 0; // 1 mma.sync, 2 tcgen05
+thread_local int g_last_prefill_kernel = 0; // 1 mma.sync, 2 tcgen05, 3 tcgen05 persistent
 std::atomic<int> g_decode_chunk{0};
 std::atomic<int> g_prefill_kernel{0};
 std::atomic<int> g_decode_early{0};
@@ -133,6 +133,16 @@ bool small_m(int m, int group) { return static_cast<long>(m) * group <= 16; }
 int run_prefill(const PrefillParams &p, bool bf16, cudaStream_t stream) {
   const int which = g_prefill_kernel.load();
   cudaError_t e;
+  if (which == 3) {   // opt-in: measured slower than the kernel below at every size tried
+    e = launch_attn_prefill_tc5p(p, bf16, stream);
+    if (e == cudaSuccess) {
+      g_launches += 1;
+      g_last_prefill_kernel = 3;
+      return GPU_OPS_OK;
+    }
+    if (e != cudaErrorNotSupported || which == 3) return cuda_fail(e, "persistent tcgen05 prefill attention launch");
+    (void)cudaGetLastError();
+  }
   if (which != 1) {
     e = launch_attn_prefill_tc5(p, bf16, stream);
     if (e == cudaSuccess) {
@@ -953,7 +963,7 @@ int gpu_attn_set_decode_early_prefetch(int on) {
 }
 
 int gpu_attn_set_prefill_kernel(int which) {
-  if (which < 0 || which > 2) return fail(GPU_OPS_E_INVALID, "prefill kernel selector %d", which);
+  if (which < 0 || which > 3) return fail(GPU_OPS_E_INVALID, "prefill kernel selector %d", which);
   g_prefill_kernel.store(which);
   return GPU_OPS_OK;
 }

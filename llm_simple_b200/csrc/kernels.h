@@ -212,6 +212,10 @@ cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStrea
 // tcgen05 / TMEM / TMA kernel; same contract.  Returns cudaErrorNotSupported if
 // the geometry cannot be described by its tensor maps.
 cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStream_t stream);
+// The same kernel in persistent form (one CTA per SM, work items handed out through a counter in
+// global memory, epilogue through a TMA tensor store); same contract.  Also returns
+// cudaErrorNotSupported on a capturing stream.
+cudaError_t launch_attn_prefill_tc5p(const PrefillParams &p, bool bf16, cudaStream_t stream);
 // Tensor maps are pure functions of (base, geometry): a small per-thread cache of the most recent
 // ones saves the driver call on repeated launches (a layer calls with the same buffers every step).
 struct TensorMapKey {

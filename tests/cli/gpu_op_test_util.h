@@ -76,14 +76,25 @@ struct Report {
   size_t worst = 0;
   bool all_close = false; // the reference tests' verdict (1e-3 abs or 1e-3 rel)
   bool within_bar = false; // max-abs <= 1e-2 and mean-abs <= 1e-3
+  // elements further than 1e-2 from the golden, and how many of those are also further than one
+  // ulp of the 16-bit type at the golden's magnitude (bf16 values of magnitude >= 2 lie 1.6e-2
+  // apart, so a correctly rounded result of a differently ordered sum can land on the neighbour)
+  size_t above = 0, beyond = 0;
+  bool within_bound() const { return mean_abs <= 1e-3 && beyond == 0; }
 };
 
-inline Report compare(const std::vector<float> &out, const std::vector<float> &golden) {
+inline Report compare(const std::vector<float> &out, const std::vector<float> &golden, int dt = DT_FLOAT16) {
   Report r;
   double sum = 0;
+  const int mant = dt == DT_BFLOAT16 ? 7 : 10;
   for (size_t i = 0; i < out.size(); ++i) {
     const double d = std::fabs(static_cast<double>(out[i]) - golden[i]);
     sum += d;
+    if (d > 1e-2) {
+      ++r.above;
+      const double mag = std::fmax(std::fabs(static_cast<double>(golden[i])), std::ldexp(1.0, -14));
+      if (!(d <= std::ldexp(1.0, static_cast<int>(std::floor(std::log2(mag))) - mant))) ++r.beyond;
+    }
     if (d > r.max_abs) {
       r.max_abs = d;
       r.worst = i;

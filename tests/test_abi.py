@@ -58,3 +58,20 @@ def test_host_side_validation_needs_no_gpu():
     assert L.gpu_attn_set_decode_chunk(0) == 0
     assert L.gpu_flash_attn_layer(None, None, None, None, 4, 4, 0, 2, 64, 4, None) == -2
     assert L.gpu_attn_decode_workspace_bytes(None, 10) == 0
+
+
+def test_reference_named_overloads_compile_and_link():
+    """include/npu_ops_compat.hpp: the reference's operator names (prebuild/npu_ops.h:6-18, :27-30, :39-47) with
+    its argument order, DataType and the stream by reference.  The test program written with those names compiles
+    and links against the library here, without a GPU (it runs in the GPU suite)."""
+    import subprocess
+    cli = os.path.join(ROOT, "tests", "cli")
+    env = dict(os.environ)
+    env.pop("CXX", None)
+    subprocess.check_call(["make", "-C", cli, "bin/npu_names_main"], env=env, stdout=subprocess.DEVNULL)
+    assert os.path.exists(os.path.join(cli, "bin", "npu_names_main"))
+    text = open(os.path.join(ROOT, "include", "npu_ops_compat.hpp")).read()
+    for name in ("npu_flash_attn_layer", "npu_flash_attn_gqa_layer", "npu_flash_attn_opt_prefill_layer",
+                 "npu_split_qkv_layer", "npu_rope_layer", "npu_rope_single_layer"):
+        assert re.search(r"inline void %s\(" % name, text), name
+    assert text.count("aclrtStream &stream") == 6

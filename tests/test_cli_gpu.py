@@ -52,3 +52,15 @@ def test_flash_attn_main(binaries, args):
 def test_rope_single_layer_main(binaries, args):
     out = run(os.path.join(binaries, "rope_single_layer_main"), *args)
     assert "bit-identical: yes" in out
+
+
+@pytest.mark.parametrize("args", [
+    ("--arch", "qwen2"),                                                   # 12 query heads on 2 KV heads, bf16, neox pairs
+    ("--arch", "qwen2", "--kv_head_num", 8, "--group_size", 5, "--prompt", 700, "--steps", 3),
+    ("--arch", "llama2"),                                                  # 8 heads MHA, fp16, interleaved pairs
+    ("--arch", "llama2", "--kv_head_num", 32, "--prompt", 256, "--dtype", "bfloat16"),
+])
+def test_attention_section_with_reference_names(binaries, args):
+    """The reference's call sequence under its own operator names (include/npu_ops_compat.hpp)."""
+    out = run(os.path.join(binaries, "npu_names_main"), *args)
+    assert "caches bit-identical to the checker: yes" in out and "error handler calls: 1" in out

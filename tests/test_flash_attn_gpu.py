@@ -25,7 +25,7 @@ def ops():
     return o
 
 
-@pytest.fixture(params=[1, 2], ids=["mma", "tcgen05"])
+@pytest.fixture(params=[1, 2, 3], ids=["mma", "tcgen05", "tcgen05-persistent"])
 def prefill_kernel(request, ops):
     ops.gpu_attn_set_prefill_kernel(request.param)
     yield request.param

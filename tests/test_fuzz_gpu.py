@@ -36,7 +36,7 @@ def _attn_cases(n_cases, seed):
 
 
 @pytest.mark.parametrize("case", _attn_cases(24, 20250), ids=lambda c: "m%d_o%d_g%d_kv%d_dt%d" % c[1:])
-@pytest.mark.parametrize("kernel", [1, 2], ids=["mma", "tcgen05"])
+@pytest.mark.parametrize("kernel", [1, 2, 3], ids=["mma", "tcgen05", "tcgen05-persistent"])
 def test_random_gqa_shapes(ops, kernel, case):
     i, m, offset, g, kvh, dt = case
     n = m + offset
@@ -96,7 +96,7 @@ def test_random_ragged_decode(ops, seed, layout):
 
 
 @pytest.mark.parametrize("dt", [FP16, BF16])
-@pytest.mark.parametrize("kernel", [1, 2], ids=["mma", "tcgen05"])
+@pytest.mark.parametrize("kernel", [1, 2, 3], ids=["mma", "tcgen05", "tcgen05-persistent"])
 def test_wide_dynamic_range_scores(ops, kernel, dt):
     """Keys whose norm grows along the sequence: the row maximum keeps rising by large steps, so the
     accumulator is rescaled many times (and, below the threshold, not rescaled) within one row."""

@@ -104,7 +104,7 @@ def test_paged_append_then_decode_matches_flat(ops, dt, neox, theta, page_size, 
 
 
 @pytest.mark.parametrize("dt", [FP16, BF16])
-@pytest.mark.parametrize("page_size,kernel", [(64, 0), (128, 2), (256, 2), (128, 1)])
+@pytest.mark.parametrize("page_size,kernel", [(64, 0), (128, 2), (256, 2), (128, 1), (128, 3), (256, 3)])
 def test_paged_chunked_prefill_matches_flat(ops, dt, page_size, kernel):
     """Two prefill chunks (offset 0, then offset m1) over a paged cache whose never-written rows hold
     NaN: the output equals the flat-cache output bit for bit and the NaN rows are never seen.
@@ -121,7 +121,7 @@ def test_paged_chunked_prefill_matches_flat(ops, dt, page_size, kernel):
     tab_d = torch.from_numpy(tab).cuda()
     pages = ops.make_pages(table, page_size, kvh * page_size * D, n_pages)
     # the flat reference runs on the kernel the paged call will end up on
-    flat_kernel = 1 if (kernel == 1 or page_size < 128) else 2
+    flat_kernel = 1 if (kernel == 1 or page_size < 128) else (kernel or 3)
     try:
         off = 0
         for c, m in enumerate((m1, m2)):
