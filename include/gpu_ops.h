@@ -412,7 +412,7 @@ int gpu_attn_set_decode_chunk(int positions);
  * 2 = tcgen05 kernel, one CTA per 256 query rows, 3 = tcgen05 kernel in
  * persistent form (one CTA per SM that takes work items from a counter, output
  * through a TMA tensor store; same bits as 2, measured slower, opt-in only; not
- * on a capturing stream).  Automatic = 2, else 1 where the tensor maps cannot
+ * on a capturing stream; its first call on a device allocates 2 KB of counters).  Automatic = 2, else 1 where the tensor maps cannot
  * describe the geometry.  Process-wide; for tests and measurements. */
 int gpu_attn_set_prefill_kernel(int which);
 

@@ -22,7 +22,8 @@
 //                 max / sum in the log2 domain, P written back over S as packed
 //                 16-bit pairs (tcgen05.st); O is only rescaled when the running
 //                 max has grown by more than 2^8 since the last rescale;
-//                 epilogue O / l -> global memory
+//                 epilogue O / l -> swizzled staging tile in shared memory -> one TMA
+//                 tensor store per tile (rows beyond m clipped by the tensor map)
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each; P_X aliases
 // the first 64 columns of S_X.
 //
@@ -57,7 +58,8 @@ constexpr uint32_t kTileBytes = 2 * kHalfTile;   // [128][128] 16-bit
 constexpr uint32_t kSmemQ = 0;                   // Q_A, Q_B
 constexpr uint32_t kSmemK = kSmemQ + 2 * kTileBytes;
 constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
-constexpr uint32_t kSmemBar = kSmemV + kStages * kTileBytes;
+constexpr uint32_t kSmemStg = kSmemV + kStages * kTileBytes;   // output staging tile, used by tile A, then by tile B
+constexpr uint32_t kSmemBar = kSmemStg + kTileBytes;
 constexpr uint32_t kSmemTotal = kSmemBar + 256 + 1024; // barriers + slack for 1024-byte alignment
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256;       // S_X at kColS + 128 X, O_X at kColO + 128 X
@@ -65,7 +67,7 @@ constexpr float kRescaleThreshold = 8.0f;        // log2 domain
 
 // barrier slots (8 bytes each) inside the barrier block; X = 0 (tile A) or 1 (tile B)
 enum { BAR_Q = 0, BAR_KFULL = 1, BAR_KEMPTY = 3, BAR_VFULL = 5, BAR_VEMPTY = 7, BAR_SFULL = 9, BAR_PREADY = 11,
-       BAR_ODONE = 13, BAR_PHALF = 15, BAR_QB = 17, BAR_COUNT = 18 };
+       BAR_ODONE = 13, BAR_PHALF = 15, BAR_QB = 17, BAR_STGWR = 18, BAR_STGFREE = 20, BAR_COUNT = 21 };
 
 struct Params {
   void *out;
@@ -83,7 +85,9 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k_tail,
-                        const __grid_constant__ CUtensorMap map_v_tail, Params p) {
+                        const __grid_constant__ CUtensorMap map_v_tail,
+                        const __grid_constant__ CUtensorMap map_o,
+                        Params p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -155,7 +159,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar(BAR_PREADY + s), 128);
       mbar_init(bar(BAR_ODONE + s), 1);
       mbar_init(bar(BAR_PHALF + s), 128);
+      mbar_init(bar(BAR_STGWR + s), 128);
     }
+    mbar_init(bar(BAR_STGFREE), 1);
     *abort_flag = 0;
     fence_barrier_init();
     // The first loads leave before TMEM is allocated and the other warps are released, so
@@ -355,24 +361,48 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (ok && ntx > 0)
       ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + x), (ntx - 1) & 1, abort_flag, p.error_flag, 9));
     if (ok && ntx > 0) {
+      // O / l leaves through a swizzled [128][128] staging tile and one TMA tensor store (two boxes; rows
+      // beyond m clipped by the tensor map) instead of 16-byte stores of 32 different rows per warp
+      // instruction.  Tile A always finishes first (it has no more KV tiles than tile B); tile B waits until
+      // A's store has read the tile.
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      T *dst = static_cast<T *>(p.out) + b * p.out_seq + static_cast<long>(row) * p.out_tok + h * kHeadDim;
+      const bool elected = quad == 0 && lane == 0;
+      if (x == 1 && !__all_sync(0xffffffffu, mbar_wait(bar(BAR_STGFREE), 0, abort_flag, p.error_flag, 13))) ok = false;
+      if (ok) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int trow = quad * 32 + lane;
+        const uint32_t stg_row = smem_base + kSmemStg + trow * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tc_ld32(ocol + 32 * c, o);
-        tc_wait_ld();
-        if (row < p.m) {
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tc_ld32(ocol + 32 * c, o);
+          tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 u;
-            u.x = Elem<T>::pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-            u.y = Elem<T>::pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            u.z = Elem<T>::pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-            u.w = Elem<T>::pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-            *reinterpret_cast<uint4 *>(dst + 32 * c + i) = u;
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w0 = Elem<T>::pack(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+            uint32_t w1 = Elem<T>::pack(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+            uint32_t w2 = Elem<T>::pack(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+            uint32_t w3 = Elem<T>::pack(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            // element d = 32 c + 8 i: half tile c / 2, 16-byte chunk (c & 1) * 4 + i, swizzled by the row
+            const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + i) ^ static_cast<uint32_t>(trow & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg_row + (c >> 1) * kHalfTile + (chunk << 4)),
+                         "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                         : "memory");
           }
+        }
+        fence_proxy_async_smem();   // the tensor store reads what this thread wrote
+        mbar_arrive(bar(BAR_STGWR + x));
+        if (elected && mbar_wait(bar(BAR_STGWR + x), 0, abort_flag, p.error_flag, 14)) {
+          asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
+                       "r"(smem_base + kSmemStg), "r"(0), "r"(h), "r"(trow0), "r"(b)
+                       : "memory");
+          asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
+                       "r"(smem_base + kSmemStg + kHalfTile), "r"(64), "r"(h), "r"(trow0), "r"(b)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          if (x == 0) mbar_arrive(bar(BAR_STGFREE));
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
       }
     }
@@ -493,6 +523,8 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   CUtensorMap mq, mk, mv, mk_tail, mv_tail;
   // q: (d, head, token, seq); k/v: (d, pos, kv_head, seq), or (d, pos in page, kv_head, page) over a pool
   if (!make_tensor_map_4d(&mq, bf16, p.q, g.n_heads, p.m, g.batch, kHeadDim, g.q_tok, g.q_seq, 1, kBM)) return cudaErrorNotSupported;
+  CUtensorMap mo;   // out: (d, head, token, seq), like q
+  if (!make_tensor_map_4d(&mo, bf16, p.out, g.n_heads, p.m, g.batch, kHeadDim, g.out_tok, g.out_seq, 1, kBM)) return cudaErrorNotSupported;
   if (p.pg.table) {
     const int page_size = 1 << p.pg.page_shift;
     if (page_size < kBN) return cudaErrorNotSupported; // a K / V tile of 128 positions must lie inside one page
@@ -541,9 +573,9 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
     if (known) attr_set[bf16 ? 1 : 0][dev] = true;
   }
   if (bf16)
-    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
+    attn_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, mo, kp);
   else
-    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, kp);
+    attn_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, mk_tail, mv_tail, mo, kp);
   return cudaGetLastError();
 }
 

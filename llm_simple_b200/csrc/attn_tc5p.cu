@@ -11,9 +11,9 @@
 // Inside an item the kernel is the non-persistent one (attn_tc5.cu): TMA producer
 // lane (warp 0), MMA-issuing lane (warp 1; tcgen05.mma, accumulators in tensor
 // memory), two groups of four softmax warps (4-7 tile A, 8-11 tile B) with one
-// thread per query row; one lane each of warps 2 and 3 issues the tensor stores
-// of tile A and of tile B.  What the persistent form adds is the overlap ACROSS
-// items:
+// thread per query row; one lane of warp 3 issues the tensor stores of both
+// tiles (warp 2 only gives its registers away).  What the persistent form adds is
+// the overlap ACROSS items:
 //   * tensor memory, barriers and tensor maps are set up once per CTA;
 //   * the producer runs ahead: the next item's Q tiles are loaded as soon as the
 //     last Q.K^T of the current item has read the old ones, and K / V tiles of the
@@ -40,7 +40,8 @@
 // The counter: two words {next item, CTAs done} per launch, zero before the
 // launch; the last CTA to finish zeroes them again.  The host hands each stream
 // its own small set of counter pairs (launches on one stream run one after the
-// other), see launch_attn_prefill_tc5p.
+// other), see launch_attn_prefill_tc5p; the 2 KB that hold them are the one
+// allocation this library makes inside an operator call (first use per device).
 //
 // Reference semantics: tests/flash_attn_test.cpp:106-192 (mask col > row+offset,
 // scale 1/sqrt(D) folded into the exponent, O = softmax(S).V, out [m][H*D]).
