@@ -18,24 +18,31 @@
 //   * the producer runs ahead: the next item's Q tiles are loaded as soon as the
 //     last Q.K^T of the current item has read the old ones, and K / V tiles of the
 //     next item follow the last ones of the current item through the same rings;
-//   * the MMA lane issues the next item's first Q_X.K^T right behind the last
-//     P_X.V of the current one, so that S_X is there when the softmax warps of X
-//     come back from their epilogue;
+//   * the MMA lane issues the next item's first Q_A.K^T and Q_B.K^T right behind
+//     the current item's last P.V, so that S_A and S_B are there when the softmax
+//     warps come back from their epilogue; per item its loop is the one of the
+//     non-persistent kernel (every item starts on an even slot of the K / V ring,
+//     an odd tile count is padded with an empty slot, so that tile j of an item
+//     always lives in stage j & 1);
 //   * the epilogue leaves through shared memory: O / l is written as a swizzled
 //     [128][128] 16-bit tile and stored with one TMA tensor store (two boxes),
 //     rows beyond m clipped by the tensor map, instead of 16-byte stores of 32
 //     different rows per warp instruction.
 //
 // Status: same bits as the non-persistent kernel on every case tried, but slower
-// (cfg3-shaped layer 0.45 against 0.41 ms, long rows 2.68 against 2.19 ms), and
+// (cfg3-shaped layer 0.46 against 0.39 ms, long rows 2.69 against 2.21 ms), and
 // therefore opt-in.  Time stamps taken inside both kernels show where: the softmax
-// warps are as fast here (1690 against 1800 cycles per tile), but the MMA-issuing
-// lane needs about 90 cycles per MMA where the tensor pipe needs 64, so the lane,
-// not the pipe, paces the kernel (a pair of tiles every 3900 cycles against 3290).
-// The cause was not found; ruled out by variant builds: register budgets, the item
-// ring and counter, the staging tile and store lane, the grid shape, the size and
-// layout of shared memory, code size, polling style, and whether tile counts and
-// ring stages are known to the compiler to be warp-uniform.
+// warps are as fast here (1690 against 1800 cycles per tile), but the products take
+// longer to come back: eight Q.K^T MMAs and their commits occupy the issuing lane
+// for 720-760 cycles against 540, so the lane, not the softmax, paces the kernel (a
+// pair of tiles every 3900 cycles against 3290).  The cause was not found.  Ruled
+// out by variant builds: register budgets, the item ring and counter, the staging
+// tile and store lane, the grid shape, the size and layout of shared memory,
+// polling style, the structure of the issuing loop (the walk of the non-persistent
+// kernel, a whole warp walking it, one flat loop over ring tiles, two issuing
+// lanes) and whether tile counts and ring stages are known to be warp-uniform.
+// Hot code size matters (two alternating copies of the softmax loop cost the
+// non-persistent kernel 9 % on short rows and 2 % on long ones), but not enough.
 //
 // The counter: two words {next item, CTAs done} per launch, zero before the
 // launch; the last CTA to finish zeroes them again.  The host hands each stream
@@ -279,30 +286,35 @@ attn_prefill_tc5p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer + item dispenser
       Item it = decode_item(p, kFirstItem);
-      uint32_t g = 0;                 // K / V tiles streamed so far
+      uint32_t g = 0;                 // ring slots used so far; every item starts on an even one (stage 0)
       uint32_t qcnt_a = 1, qcnt_b = it.has_b ? 1u : 0u;   // Q tiles loaded so far
       bool ok = true;
+      // K and V of tile j into ring slot `slot`, each as soon as its stage has been released
+      auto load_slot = [&](const Item &item, int j, uint32_t slot) -> bool {
+        const int s = slot % kStages;
+        const uint32_t ph = (slot / kStages) & 1;
+        if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1)) return false;
+        load_kv_tile(item, j, slot, true);
+        if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2)) return false;
+        load_kv_tile(item, j, slot, false);
+        return true;
+      };
       for (int e = 1; ok; ++e) {
         // take the next item now; its number is needed only after this item's first loads are on their way
         const int next_item = uniform(static_cast<int>(kGridSize + atomicAdd(p.ticket, 1u)));
         if (e > 1) {               // the first item's first loads left before the set-up barrier
-          const int s = g % kStages;
-          const uint32_t ph = (g / kStages) & 1;
           if (!(ok = mbar_wait(bar(BAR_QEMPTY + 0), (qcnt_a & 1) ^ 1, abort_flag, p.error_flag, 13))) break;
           load_q_tile(it, 0);
           ++qcnt_a;
-          if (!(ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1))) break;
-          load_kv_tile(it, 0, g, true);
-          if (!(ok = mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2))) break;
-          load_kv_tile(it, 0, g, false);
+          if (!(ok = load_slot(it, 0, g))) break;
           if (it.has_b) {
             if (!(ok = mbar_wait(bar(BAR_QEMPTY + 1), (qcnt_b & 1) ^ 1, abort_flag, p.error_flag, 14))) break;
             load_q_tile(it, 1);
             ++qcnt_b;
           }
         }
-        // Publish the next item before the rest of this one: the MMA lane looks one item ahead, and
-        // nothing up to here waited for anything it issues after reading this entry.
+        // Publish the next item before the rest of this one: the MMA lane reads it at the end of this
+        // item, and nothing up to here waited for anything it issues after that.
         {
           const int slot = (e - 1) % kItemRing;   // entries are numbered from 1
           if (!(ok = mbar_wait(bar(BAR_ITEMEMPTY + slot), (((e - 1) / kItemRing) & 1) ^ 1, abort_flag, p.error_flag, 15))) break;
@@ -310,15 +322,20 @@ attn_prefill_tc5p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           mbar_arrive(bar(BAR_ITEMFULL + slot));
         }
         for (int j = 1; j < it.nt; ++j) {
-          const int s = (g + j) % kStages;
-          const uint32_t ph = ((g + j) / kStages) & 1;
-          if (!(ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 1))) break;
-          load_kv_tile(it, j, g + j, true);
-          if (!(ok = mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_flag, p.error_flag, 2))) break;
-          load_kv_tile(it, j, g + j, false);
+          if (!(ok = load_slot(it, j, g + j))) break;
         }
         if (!ok) break;
         g += it.nt;
+        if (g & 1) {
+          // An odd number of tiles: one empty slot keeps the next item on stage 0, so that the MMA lane's
+          // stage index is its loop counter's parity.  The slot is "filled" by a plain arrival.
+          const uint32_t ph = (g / kStages) & 1;
+          if (!(ok = mbar_wait(bar(BAR_KEMPTY + 1), ph ^ 1, abort_flag, p.error_flag, 1))) break;
+          mbar_arrive(bar(BAR_KFULL + 1));
+          if (!(ok = mbar_wait(bar(BAR_VEMPTY + 1), ph ^ 1, abort_flag, p.error_flag, 2))) break;
+          mbar_arrive(bar(BAR_VFULL + 1));
+          ++g;
+        }
         it = decode_item(p, next_item);
         if (!it.valid) break;
       }
@@ -331,20 +348,17 @@ attn_prefill_tc5p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const uint32_t dk0 = smem_desc_lo(smem_base + kSmemK, 16);
       const uint32_t dv0 = smem_desc_lo(smem_base + kSmemV, kHalfTile);
       constexpr uint32_t kTileStep = kTileBytes >> 4; // one tile further, in descriptor address units
-      // running parities of the per-tile barriers of query tile A and B: products P.V issued so far
-      // and items whose Q_X has been consumed so far
-      uint32_t pv_par_a = 0, pv_par_b = 0, q_par_a = 0, q_par_b = 0;
-      // S_X = Q_X . K[g]^T.  first_qk: the item's first product (wait for its Q_X); last_qk: the item's
-      // last reader of Q_X; last_reader: the last reader of K tile g, which frees the stage.
-      auto issue_qk = [&](auto X, uint32_t g, bool first_qk, bool last_qk, bool last_reader) -> bool {
-        constexpr int x = decltype(X)::value;
-        const uint32_t s = g % kStages;
-        if (first_qk) {
-          uint32_t &q_par = x ? q_par_b : q_par_a;
-          if (!mbar_wait(bar(BAR_QFULL + x), q_par, abort_flag, p.error_flag, 3 + 8 * x)) return false;
-          q_par ^= 1u;
-        }
-        if (!mbar_wait(bar(BAR_KFULL + s), (g / kStages) & 1, abort_flag, p.error_flag, 4)) return false;
+      // Per item the loop below is the one of the non-persistent kernel: tile j of the item lives in ring
+      // stage j & 1 (every item starts on an even ring slot), so stages and shared-memory descriptors
+      // derive from the loop counter alone; what runs across items -- ring slots used, tiles per query
+      // tile, Q tiles consumed -- only enters the barrier parities.
+      uint32_t g0 = 0;                 // ring slot of the current item's tile 0 (even)
+      uint32_t tiles_a = 0, tiles_b = 0, q_par_a = 0, q_par_b = 0;
+      // S_X = Q_X . K[j]^T; `last` marks the last reader of K[j], which frees the stage; last_qk the item's
+      // last reader of Q_X, which frees the Q tile for the producer
+      auto issue_qk = [&](int x, int j, bool last, bool last_qk) -> bool {
+        const int s = j % kStages;
+        if (!mbar_wait(bar(BAR_KFULL + s), ((g0 + j) / kStages) & 1, abort_flag, p.error_flag, 4)) return false;
         tc_fence_after();
         const uint32_t d = tmem + kColS + 128 * x;
         const uint32_t dq = dq0 + x * kTileStep, dk = dk0 + s * kTileStep;
@@ -354,82 +368,83 @@ attn_prefill_tc5p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           const uint32_t ko = (k >> 2) * kHalfStep + (k & 3) * 2; // 16 elements = 32 bytes per step
           tc_mma_ss(d, dq + ko, dk + ko, kDescHi, idesc_qk, k > 0);
         }
-        if (last_reader) tc_commit(bar(BAR_KEMPTY + s));
+        if (last) tc_commit(bar(BAR_KEMPTY + s));
         if (last_qk) tc_commit(bar(BAR_QEMPTY + x));
         tc_commit(bar(BAR_SFULL + x));
         return true;
       };
-      // O_X (+)= P_X . V[g]; first_pv: the item's first product overwrites O_X (whose previous content the
-      // softmax warps of X read out before they produced this P_X); last_reader frees the V stage.
-      auto issue_pv = [&](auto X, uint32_t g, bool first_pv, bool last_reader) -> bool {
-        constexpr int x = decltype(X)::value;
-        const uint32_t s = g % kStages;
-        uint32_t &pv_par = x ? pv_par_b : pv_par_a;
+      // O_X += P_X . V[j] ; `last` marks the last reader of V[j]
+      auto issue_pv = [&](int x, int j, bool last) -> bool {
+        const int s = j % kStages;
+        const uint32_t par = ((x ? tiles_b : tiles_a) + j) & 1;
         // The softmax warps publish the first 64 positions of P before they start on the
         // other 64, so that half of this product overlaps their remaining exponentials.
-        if (!mbar_wait(bar(BAR_PHALF + x), pv_par, abort_flag, p.error_flag, 10)) return false;
-        if (!mbar_wait(bar(BAR_VFULL + s), (g / kStages) & 1, abort_flag, p.error_flag, 6)) return false;
+        if (!mbar_wait(bar(BAR_PHALF + x), par, abort_flag, p.error_flag, 10)) return false;
+        if (!mbar_wait(bar(BAR_VFULL + s), ((g0 + j) / kStages) & 1, abort_flag, p.error_flag, 6)) return false;
         tc_fence_after();
         const uint32_t pcol = tmem + kColS + 128 * x, ocol = tmem + kColO + 128 * x;
         const uint32_t dv = dv0 + s * kTileStep;
-        const uint32_t acc0 = first_pv ? 0u : 1u;
+        const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           // 16 positions per step: 8 TMEM columns of packed P, 16 rows (2048 B) of V
           tc_mma_ts(ocol, pcol + 8 * k, dv + k * (2048 >> 4), kDescHi, idesc_pv, k > 0 ? 1u : acc0);
         }
-        if (!mbar_wait(bar(BAR_PREADY + x), pv_par, abort_flag, p.error_flag, 5)) return false;
+        if (!mbar_wait(bar(BAR_PREADY + x), par, abort_flag, p.error_flag, 5)) return false;
         tc_fence_after();
 #pragma unroll
         for (int k = 4; k < 8; ++k) tc_mma_ts(ocol, pcol + 8 * k, dv + k * (2048 >> 4), kDescHi, idesc_pv, 1u);
-        if (last_reader) tc_commit(bar(BAR_VEMPTY + s));
+        if (last) tc_commit(bar(BAR_VEMPTY + s));
         tc_commit(bar(BAR_ODONE + x));
-        pv_par ^= 1u;
         return true;
       };
-      // The items of this CTA form one stream of tiles per X.  Per KV tile j of the current item the
-      // lane issues  P.V(A, j)  Q.K(A, next)  P.V(B, j)  Q.K(B, next),  where `next` is tile j + 1 of
-      // the item or, behind X's last tile, tile 0 of the NEXT item (whose Q_X and first K tile the
-      // producer has loaded by then; an X the current item lacks looks ahead at the item's last step,
-      // not earlier: the K ring cannot reach the next item before this one's tiles have been read).
-      // Tile B (when present) reads every KV tile that A reads, and reads it after A.  The walk starts
-      // from an empty item in front of the first one, so that the first item's Q.K^T products come
-      // from the same code.
-      int cur_nt_a = 0, cur_nt_b = 0;            // an empty item
-      Item nxt = decode_item(p, kFirstItem);
-      uint32_t g0 = 0;
-      int e = 0;
-      bool ok = true;
-      while (ok) {
-        const int cur_nt = max(cur_nt_a, cur_nt_b);
-        const bool cur_has_b = cur_nt_b > 0;
-        const uint32_t gn = g0 + cur_nt;             // first K / V tile of the next item
-        const int steps = max(cur_nt, 1);
-        auto step = [&](auto X, int j) -> bool {
-          constexpr int x = decltype(X)::value;
-          const int ntx = x ? cur_nt_b : cur_nt_a;
-          const bool last_reader = x == 1 || !cur_has_b;
-          if (j < ntx && !issue_pv(X, g0 + j, j == 0, last_reader)) return false;
-          // the next Q.K^T of X: in this item, or the first one of the next item
-          const bool same = j + 1 < ntx;
-          const bool ahead = !same && (j + 1 == ntx || (ntx == 0 && j + 1 == steps)) && nxt.valid && (x == 0 || nxt.has_b);
-          if (!same && !ahead) return true;
-          const int nx = x ? nxt.nt_b : nxt.nt_a;
-          return issue_qk(X, same ? g0 + j + 1 : gn, ahead, same ? j + 2 == ntx : nx == 1,
-                          same ? last_reader : (x == 1 || !nxt.has_b));
-        };
-        for (int j = 0; ok && j < steps; ++j) {
-          ok = step(std::integral_constant<int, 0>{}, j);
-          if (ok) ok = step(std::integral_constant<int, 1>{}, j);
+      // the first Q.K^T products of an item (tile 0, stage 0), once its Q tiles are there
+      auto first_products = [&](const Item &it) -> bool {
+        if (!mbar_wait(bar(BAR_QFULL + 0), q_par_a, abort_flag, p.error_flag, 3)) return false;
+        q_par_a ^= 1u;
+        if (!issue_qk(0, 0, !it.has_b, it.nt_a == 1)) return false;
+        if (it.has_b) {
+          if (!mbar_wait(bar(BAR_QFULL + 1), q_par_b, abort_flag, p.error_flag, 11)) return false;
+          q_par_b ^= 1u;
+          if (!issue_qk(1, 0, true, it.nt_b == 1)) return false;
         }
-        if (!ok || !nxt.valid) break;
-        g0 = gn;
-        cur_nt_a = nxt.nt_a;
-        cur_nt_b = nxt.nt_b;
-        // the item after that one (the producer publishes it once its counter read has returned)
-        const int nid = fetch_item(++e);
-        ok = nid >= 0;
-        nxt = decode_item(p, ok ? nid : p.n_items);
+        return true;
+      };
+      Item cur = decode_item(p, kFirstItem);
+      bool ok = first_products(cur);
+      for (int e = 1; ok; ++e) {
+        const int nt = cur.nt, nt_a = cur.nt_a, nt_b = cur.nt_b;
+        const bool has_b = cur.has_b;
+        // tile B (when present) reads every KV tile that A reads, and reads it after A
+        for (int j = 0; ok && j < nt; ++j) {
+          if (j < nt_a) {
+            ok = issue_pv(0, j, !has_b);
+            if (ok && j + 1 < nt_a) ok = issue_qk(0, j + 1, !has_b, j + 2 == nt_a);
+          }
+          if (ok && has_b) {
+            ok = issue_pv(1, j, true);
+            if (ok && j + 1 < nt_b) ok = issue_qk(1, j + 1, true, j + 2 == nt_b);
+          }
+        }
+        if (!ok) break;
+        tiles_a += nt_a;
+        tiles_b += nt_b;
+        g0 += nt;
+        if (g0 & 1) {
+          // the empty slot that pads an odd tile count: release it behind the products issued so far
+          if (!(ok = mbar_wait(bar(BAR_KFULL + 1), (g0 / kStages) & 1, abort_flag, p.error_flag, 4))) break;
+          tc_commit(bar(BAR_KEMPTY + 1));
+          if (!(ok = mbar_wait(bar(BAR_VFULL + 1), (g0 / kStages) & 1, abort_flag, p.error_flag, 6))) break;
+          tc_commit(bar(BAR_VEMPTY + 1));
+          ++g0;
+        }
+        // The next item's first products go out right here, behind this item's last P.V: its S_A and S_B
+        // are being computed while the softmax warps are in their epilogue.
+        const int nid = fetch_item(e);
+        if (nid < 0) break;
+        cur = decode_item(p, nid);
+        if (!cur.valid) break;
+        ok = first_products(cur);
       }
     } else if (warp == 3 && lane == 0) {
       // ---------------------------------------------------------- tensor stores of both tiles' output
