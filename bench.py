@@ -533,6 +533,12 @@ def main():
     sampler = ClockSampler(env.local_rank).start()
     for _ in range(max(args.warmup, 3)):
         run_step()
+    # keep the load up until the sampler has delivered its first row (nvidia-smi takes up to a few seconds to
+    # start on a box with many GPUs), so that the timed region below is always covered by samples
+    t_wait = time.monotonic()
+    while not sampler.rows and sampler.proc is not None and time.monotonic() - t_wait < 5.0:
+        run_step()
+        torch.cuda.synchronize()
     barrier()
     with sampler as clk:
         # at least five intervals of K steps, and more until 0.3 s are covered, so that the clock

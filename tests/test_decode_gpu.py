@@ -263,3 +263,47 @@ def test_early_prefetch_gives_the_same_bits(ops):
     for l in range(layers):
         assert torch.equal(results[0][1][l].view(torch.int16), results[1][1][l].view(torch.int16))
         assert torch.equal(results[0][2][l].view(torch.int16), results[1][2][l].view(torch.int16))
+
+
+def test_understated_max_kv_len_is_reported_and_reads_nothing_beyond_its_scratch(ops):
+    """The caller's bound on the cache lengths (max_kv_len) sizes the grid and the scratch; the kernels take the
+    lengths themselves from device memory.  A sequence longer than the bound cannot be served (its last splits are
+    never launched), but the call must degrade safely: the status word reports it (code 40), the merge uses only the
+    splits that exist (the scratch is followed by NaN here: reading past it would show in the output), and the
+    context stays usable."""
+    dt, H, kvh, kv_len, chunk, max_pos = BF16, 12, 2, 700, 128, 1024
+    table = orc.init_freq_cis(D, max_pos, 1e6, dt)
+    q = rnd_bits((1, H * D), dt, 1)
+    k_new, v_new = rnd_bits((1, kvh * D), dt, 2), rnd_bits((1, kvh * D), dt, 3)
+    kc, vc = rnd_bits((1, kvh, max_pos, D), dt, 4), rnd_bits((1, kvh, max_pos, D), dt, 5)
+    desc = ops.make_desc(dt, 1, H, kvh, 1, max_pos, layout="head", is_neox=True)
+    out = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
+    lens_d = torch.tensor([kv_len], dtype=torch.int32, device="cuda")
+    understated = 640                                     # five splits of 128; the sequence needs six
+    ops.gpu_attn_set_decode_chunk(chunk)
+    try:
+        ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, understated)
+        ws = torch.full((ws_bytes // 4 + 4096,), float("nan"), dtype=torch.float32, device="cuda")
+        assert ops.gpu_ops_kernel_status() == 0
+        ops.gpu_attn_decode_layer(desc, out, None, None, dev(q, dt), dev(k_new, dt), dev(v_new, dt), dev(kc, dt),
+                                  dev(vc, dt), torch.from_numpy(table).cuda(), lens_d, None, True, understated, ws,
+                                  ws_bytes)
+        torch.cuda.synchronize()
+        assert ops.gpu_ops_kernel_status() == 40
+        assert bool(torch.isfinite(out.float()).all())
+        assert bool(torch.isnan(ws[ws_bytes // 4:]).all())    # nothing was written behind the scratch either
+    finally:
+        ops.gpu_attn_set_decode_chunk(0)
+        ops.gpu_ops_clear_kernel_status()
+    # the same call with an honest bound works afterwards
+    ws_bytes = ops.gpu_attn_decode_workspace_bytes(desc, kv_len + 1)
+    ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    kc_d, vc_d = dev(kc, dt), dev(vc, dt)
+    ops.gpu_attn_decode_layer(desc, out, None, None, dev(q, dt), dev(k_new, dt), dev(v_new, dt), kc_d, vc_d,
+                              torch.from_numpy(table).cuda(), lens_d, None, True, kv_len + 1, ws, ws_bytes)
+    torch.cuda.synchronize()
+    assert ops.gpu_ops_kernel_status() == 0
+    kc_tok = np.ascontiguousarray(kc[0].transpose(1, 0, 2)).reshape(max_pos, kvh * D)
+    vc_tok = np.ascontiguousarray(vc[0].transpose(1, 0, 2)).reshape(max_pos, kvh * D)
+    gold = oracle_decode_step(q[0], k_new[0], v_new[0], kc_tok, vc_tok, kv_len, table, H, kvh, True, dt, orc.MODE_GOLDEN)
+    assert_parity(host(out)[0], gold, dt, "after the reported call")
