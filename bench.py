@@ -919,6 +919,17 @@ def split_kv_leg(env, layers=16, reps=20):
         res[mode] = timed(step)
         outs[mode] = bits(out[0][0]).copy()
         dec.close()
+    # the all-gather exchange behind the planned decode kernel (the slice length is known on the host)
+    dec = sharding.SplitKVDecoder(desc, DT_BF16, exchange="nccl")
+    state = {"plan": None, "ws": None}
+
+    def step_planned():
+        for l in range(layers):
+            state["plan"], state["ws"] = dec.step_planned(out[l], q[l], k[l], v[l], kc[l], vc[l], tab, n_loc, pos_d,
+                                                          state["plan"], state["ws"])
+    res["nccl_planned_kernel"] = timed(step_planned)
+    outs["nccl_planned_kernel"] = bits(out[0][0]).copy()
+    dec.close()
     res["kernel_status"] = ops.gpu_ops_kernel_status()
     same = bool(np.array_equal(outs["nccl"], outs["peer"]))
     flags = [None] * world
@@ -928,6 +939,7 @@ def split_kv_leg(env, layers=16, reps=20):
                              bit_identical_nccl_vs_peer=all(flags),
                              checked="layer 0: merged output of all ranks' position slices against the checker over "
                                      "the whole 32769-position cache; both exchanges")
+        res["parity_planned_kernel"] = parity_stats(orc, outs["nccl_planned_kernel"], gold, orc.DT_BFLOAT16)
     return res
 
 

@@ -200,6 +200,31 @@ class SplitKVDecoder:
         self.dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
         ops.gpu_attn_merge_packed_layer(out, self.recv, self.world, self.rows, self.desc.head_dim, self.dt)
 
+    def step_planned(self, out, q_in, k_in, v_in, k_cache, v_cache, freqs_cis, local_len, rope_pos_dev, plan=None,
+                     workspace=None):
+        """The same step on the planned decode kernel (gpu_attn_decode_planned_layer): the length of this rank's
+        slice is known on the host (a serving loop hands out the slices), so the work partition is built from it
+        and the kernel writes (O, LSE) of every query row straight into the all-gather send buffer.  All-gather
+        exchange only.  `plan` / `workspace`: pass the ones of an earlier call with the same local_len to skip
+        rebuilding them (returned by every call)."""
+        from . import ops
+        if self.peer:
+            raise ValueError("step_planned uses the all-gather exchange")
+        tail = self.rank == self.world - 1
+        if plan is None:
+            plan = ops.DecodePlan(self.desc, [int(local_len)] * self.desc.batch, tail)
+            plan.upload()
+        if workspace is None:
+            workspace = self.torch.empty(max(plan.workspace_bytes, 16), dtype=self.torch.uint8, device="cuda")
+        o_ptr = self.send.data_ptr()
+        lse_ptr = o_ptr + self.rows * self.desc.head_dim * 4
+        ops.gpu_attn_decode_planned_layer(self.desc, None, plan, None, o_ptr, lse_ptr, q_in, k_in if tail else None,
+                                          v_in if tail else None, k_cache, v_cache, freqs_cis, rope_pos_dev, workspace,
+                                          plan.workspace_bytes)
+        self.dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        ops.gpu_attn_merge_packed_layer(out, self.recv, self.world, self.rows, self.desc.head_dim, self.dt)
+        return plan, workspace
+
     def close(self):
         if self.peer:
             self.dist.barrier(self.group)

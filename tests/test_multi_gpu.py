@@ -83,7 +83,14 @@ def _rank_main(rank, world, port, ret):
                  torch.from_numpy(table).cuda(), torch.tensor([sl_hi - sl_lo], dtype=torch.int32, device="cuda"),
                  torch.tensor([total_old], dtype=torch.int32, device="cuda"), sl_hi - sl_lo, ws, ws_bytes)
         torch.cuda.synchronize()
-        ret[rank] = (sharded, host(out))
+        # the same step on the planned decode kernel (the slice length is known on the host)
+        out_p = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
+        dec.step_planned(out_p, dev(q[:1], dt), dev(k[:1], dt), dev(v[:1], dt), dev(kl, dt), dev(vl, dt),
+                         torch.from_numpy(table).cuda(), sl_hi - sl_lo,
+                         torch.tensor([total_old], dtype=torch.int32, device="cuda"))
+        torch.cuda.synchronize()
+        assert ops.gpu_ops_kernel_status() == 0
+        ret[rank] = (sharded, host(out), host(out_p))
     finally:
         dist.destroy_process_group()
 
@@ -97,8 +104,8 @@ def test_two_ranks_head_sharding_and_split_kv_exchange():
     mp.spawn(_rank_main, args=(world, port, ret), nprocs=world, join=True)
     dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc = _case()
     single = _decode(ops, dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc)
-    sharded0, split0 = ret[0]
-    sharded1, split1 = ret[1]
+    sharded0, split0, planned0 = ret[0]
+    sharded1, split1, planned1 = ret[1]
     # head-sharded vs single device: same kernel on disjoint heads.  Where a head's cache is cut
     # between CTAs depends on how many heads share the device, so the sums may be ordered
     # differently: equal within the parity tolerance, and both ranks gathered the same bytes.
@@ -115,6 +122,8 @@ def test_two_ranks_head_sharding_and_split_kv_exchange():
     gold = orc.attn(q_r, kc_t, vc_t, 1, L + 1, L, H // kvh, kvh, D, dt, orc.MODE_GOLDEN, threads=8)
     assert_parity(split0, gold, dt, "rank 0")
     assert np.array_equal(split0, split1)
+    assert_parity(planned0, gold, dt, "rank 0, planned kernel")
+    assert np.array_equal(planned0, planned1)
 
 
 def _flow_case():
