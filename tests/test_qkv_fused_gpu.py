@@ -64,9 +64,9 @@ def test_split_qkv_rejects_bad_arguments(ops):
 @pytest.mark.parametrize("dt,neox,theta", [(FP16, False, 1e4), (BF16, True, 1e6)])
 @pytest.mark.parametrize("layout", ["token", "head"])
 @pytest.mark.parametrize("with_bias", [False, True])
-@pytest.mark.parametrize("batch,m,H,kvH,pad", [(1, 256, 32, 32, 0), (3, 5, 12, 2, 64), (8, 1, 40, 8, 0)])
+@pytest.mark.parametrize("batch,m,H,kvH,pad", [(1, 256, 32, 32, 0), (3, 5, 12, 2, 64), (8, 1, 40, 8, 0), (5, 1001, 3, 1, 128)])
 def test_fused_qkv_rope_kv_append(ops, dt, neox, theta, layout, with_bias, batch, m, H, kvH, pad):
-    max_pos = 320
+    max_pos = max(320, m + 64)
     qd, kd = H * D, kvH * D
     width = qd + 2 * kd
     row = width + pad                             # a padded row stride must be honoured

@@ -65,9 +65,9 @@ def test_rope_layer_q_and_k(ops, seq_len):
 
 @pytest.mark.parametrize("dt,neox,theta", [(FP16, False, 1e4), (BF16, True, 1e6)])
 @pytest.mark.parametrize("layout", ["token", "head"])
-@pytest.mark.parametrize("batch,m,H,kvH", [(1, 256, 32, 32), (3, 5, 12, 2), (8, 1, 40, 8)])
+@pytest.mark.parametrize("batch,m,H,kvH", [(1, 256, 32, 32), (3, 5, 12, 2), (8, 1, 40, 8), (5, 1001, 3, 1)])
 def test_fused_rope_kv_append(ops, dt, neox, theta, layout, batch, m, H, kvH):
-    max_pos = 320
+    max_pos = max(320, m + 64)
     rng = np.random.default_rng(batch * 1000 + m)
     starts = rng.integers(0, max_pos - m + 1, size=batch).astype(np.int32)
     table = orc.init_freq_cis(D, max_pos, theta, dt)
