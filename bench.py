@@ -695,7 +695,9 @@ def e2e_leg(env, cfg, lens, k_cache, v_cache, tab, H_l, kvh_l, bytes_layer_all):
            "d2h_bytes_per_step": int(layers * batch * H_l * D * 2 * env.world), "ms_per_step": head["ms_per_step"],
            "ms_per_step_spread": head["ms_per_step_spread"], "steps": steps,
            "api": "gpu_decode_step_prepare once per step + gpu_attention_layer_forward_host per layer (C ABI of the "
-                  "host layer): pinned host q/k/v row in, attention output back to pinned host memory, one stream",
+                  "host layer): pinned host q/k/v row in, attention output back to pinned host memory, one caller "
+                  "stream (the layer's default: its input copy runs on a stream of its own, so it overlaps the "
+                  "previous layer's kernels; output copy and kernels on the caller's stream)",
            "two_streams": dict(res["two_streams"], note="layers alternate between two streams: possible only because "
                                "this benchmark's layers are independent; not the headline")}
     for o in objs:

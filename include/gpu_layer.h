@@ -99,11 +99,23 @@ int gpu_attention_layer_set_shared_step(void *layer, void *step /* NULL unsets *
 
 /* The same forward with HOST buffers: qkv_host [batch][cur_size][(n_heads +
  * 2 n_kv_heads)*D] (q, k, v columns of one packed projection row; pinned memory
- * for asynchronous copies), out_host [batch][cur_size][n_heads*D].  Copies and
- * kernels are enqueued on `stream`; synchronise it before reading out_host. */
+ * for asynchronous copies), out_host [batch][cur_size][n_heads*D].  The kernels
+ * and the copy of the output are enqueued on `stream`; synchronise it before
+ * reading out_host.  The copy of the input runs on a stream the layer owns and
+ * `stream` waits for it, so that it overlaps the work `stream` still holds (the
+ * previous layer's kernels): qkv_host must hold its data when the call is made
+ * and keep it until `stream` has passed the call.  In a one-token step whose
+ * out_host is pinned memory the kernels store the output rows into out_host
+ * themselves and no copy follows them. */
 int gpu_attention_layer_forward_host(void *layer, void *out_host, const void *qkv_host, int batch,
                                      int cur_pos, int prev_pos, const int32_t *kv_len_host,
                                      gpu_stream_t stream);
+
+/* on = 0: gpu_attention_layer_forward_host copies its input on `stream` itself,
+ * behind the stream's earlier work (for a qkv_host that is filled by that work),
+ * and always copies its output from a device buffer.  on = 1 (the default): as
+ * described above.  A stream under capture always takes the input copy on itself. */
+int gpu_attention_layer_set_host_copy_overlap(void *layer, int on);
 
 /* Device-buffer entry fed from a fused projection output: qkv [batch][cur_size]
  * [(n_heads + 2 n_kv_heads)*D] on the device (the tensor npu_split_qkv_layer,

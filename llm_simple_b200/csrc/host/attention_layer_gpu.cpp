@@ -1,6 +1,7 @@
 #include "attention_layer_gpu.hpp"
 
 #include <cmath>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 
@@ -118,6 +119,12 @@ void AttentionLayerGPUImpl::UnInit() {
   staging_in_.reset();
   staging_out_.reset();
   staging_in_bytes_ = staging_out_bytes_ = 0;
+  if (in_ready_) cudaEventDestroy(in_ready_);
+  if (in_free_) cudaEventDestroy(in_free_);
+  if (copy_stream_) cudaStreamDestroy(copy_stream_); // returns at once; the stream goes when its work is done
+  in_ready_ = in_free_ = nullptr;
+  copy_stream_ = nullptr;
+  in_free_recorded_ = false;
   own_step_.reset();
   k_cache_raw_ = v_cache_raw_ = nullptr;
   freq_cis_ = nullptr;
@@ -311,15 +318,48 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
     staging_out_bytes_ = out_bytes;
   }
   cudaStream_t s = ctx.gpu_stream;
-  if (cudaMemcpyAsync(staging_in_->data_ptr, qkv_host, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
-    return GPU_OPS_E_CUDA;
+  // The input goes up on the layer's own stream, so that it does not queue behind the kernels the
+  // caller's stream still holds; a stream under capture keeps everything in its own order.
+  bool overlap = overlap_host_copies_;
+  if (overlap) {
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) overlap = false;
+  }
+  if (overlap && !copy_stream_) {
+    if (cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&in_ready_, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&in_free_, cudaEventDisableTiming) != cudaSuccess)
+      return GPU_OPS_E_CUDA;
+  }
+  if (overlap) {
+    // not before the previous call's kernels have read (prefill: rotated in place) the buffer
+    if (in_free_recorded_ && cudaStreamWaitEvent(copy_stream_, in_free_, 0) != cudaSuccess) return GPU_OPS_E_CUDA;
+    if (cudaMemcpyAsync(staging_in_->data_ptr, qkv_host, in_bytes, cudaMemcpyHostToDevice, copy_stream_) != cudaSuccess ||
+        cudaEventRecord(in_ready_, copy_stream_) != cudaSuccess || cudaStreamWaitEvent(s, in_ready_, 0) != cudaSuccess)
+      return GPU_OPS_E_CUDA;
+  } else {
+    if (cudaMemcpyAsync(staging_in_->data_ptr, qkv_host, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+      return GPU_OPS_E_CUDA;
+  }
   const char *base = static_cast<const char *>(staging_in_->data_ptr);
   const void *q = base, *k = base + cfg_.n_heads * D * 2, *v = base + (cfg_.n_heads + cfg_.n_kv_heads) * D * 2;
   int rc;
+  // A one-token step writes a few hundred KB of output rows: when out_host is pinned memory the kernels
+  // store them there themselves (the device address of the same bytes) and no copy is queued behind them.
+  void *out_dev = staging_out_->data_ptr;
+  if (ctx.cur_size == 1 && overlap_host_copies_) {
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, out_host) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer &&
+        reinterpret_cast<uintptr_t>(at.devicePointer) % 16 == 0)
+      out_dev = at.devicePointer;
+    else
+      cudaGetLastError(); // an address the runtime does not know leaves an error behind
+  }
+  const bool direct_out = out_dev != staging_out_->data_ptr;
   if (ctx.cur_size == 1) {
     // q, k, v are columns of one packed row: strides say so
     gpu_attn_desc d = MakeDesc(batch, 1, row, row, row, row);
-    rc = DecodeStepCall(d, staging_out_->data_ptr, q, k, v, kv_len_host, ctx.prev_pos, batch, s);
+    rc = DecodeStepCall(d, out_dev, q, k, v, kv_len_host, ctx.prev_pos, batch, s);
   } else {
     gpu_attn_desc d = MakeDesc(batch, ctx.cur_size, row, ctx.cur_size * row, row, ctx.cur_size * row);
     // rotate Q in place inside the staging buffer
@@ -329,8 +369,18 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
       rc = gpu_attn_prefill_layer(&d, staging_out_->data_ptr, q, k_cache_raw_, v_cache_raw_, ctx.cur_size,
                                   ctx.prev_pos, s);
   }
+  if (overlap_host_copies_) {
+    // whichever way this call's input came, the next overlapped copy must wait for these kernels
+    if (!in_free_ && cudaEventCreateWithFlags(&in_free_, cudaEventDisableTiming) != cudaSuccess) return GPU_OPS_E_CUDA;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone) {
+      if (cudaEventRecord(in_free_, s) != cudaSuccess) return GPU_OPS_E_CUDA;
+      in_free_recorded_ = true;
+    }
+  }
   if (rc) return rc;
-  if (cudaMemcpyAsync(out_host, staging_out_->data_ptr, out_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+  if (!direct_out &&
+      cudaMemcpyAsync(out_host, staging_out_->data_ptr, out_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess)
     return GPU_OPS_E_CUDA;
   return GPU_OPS_OK;
 }

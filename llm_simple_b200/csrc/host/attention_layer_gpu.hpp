@@ -125,9 +125,17 @@ public:
                    const int32_t *kv_len_host);
 
   // Host-buffer entry: q/k/v packed as [batch][cur_size][(n_heads + 2 n_kv_heads)*D]
-  // in (pinned) host memory, output to host memory; copies are enqueued on the
-  // stream around the kernels.  kv_len_host == NULL: uniform ctx.prev_pos.
+  // in (pinned) host memory, output to host memory.  The kernels and the copy of the
+  // output are enqueued on the stream.  The copy of the input runs on a stream of the
+  // layer's own and the caller's stream waits for it, so it overlaps whatever the
+  // caller's stream is still busy with (the previous layer's kernels): qkv_host must
+  // hold its data when the call is made and keep it until the stream has passed the
+  // call.  In a one-token step with out_host in pinned memory the kernels store the
+  // output rows into out_host themselves (no copy behind them).  SetHostCopyOverlap(false)
+  // puts both copies on the caller's stream, in its order; a stream that is being captured
+  // keeps the input copy on itself.  kv_len_host == NULL: uniform ctx.prev_pos.
   int ForwardHost(void *out_host, const void *qkv_host, InferenceCtx &ctx, int batch, const int32_t *kv_len_host);
+  void SetHostCopyOverlap(bool on) { overlap_host_copies_ = on; }
 
   // Per-step state shared by all layers of a model: the device array of cache
   // lengths (tokens already cached per sequence) and its maximum + 1.  While
@@ -167,6 +175,12 @@ protected:
   std::unique_ptr<DecodeStep> own_step_; // for calls that come with host lengths and no shared step
   std::shared_ptr<Tensor> staging_in_, staging_out_; // device side of ForwardHost
   size_t staging_in_bytes_{0}, staging_out_bytes_{0};
+  // ForwardHost's input copies: the layer's own stream, "input is on the device" and "the kernels
+  // have read the staging buffer" events
+  cudaStream_t copy_stream_{nullptr};
+  cudaEvent_t in_ready_{nullptr}, in_free_{nullptr};
+  bool in_free_recorded_{false};
+  bool overlap_host_copies_{true};
   const int32_t *shared_lens_{nullptr};
   int shared_max_len_{0};
   long shared_total_{0};

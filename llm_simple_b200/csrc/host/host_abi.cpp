@@ -122,6 +122,12 @@ int gpu_attention_layer_forward_host(void *layer, void *out_host, const void *qk
   return as_layer(layer)->ForwardHost(out_host, qkv_host, ctx, batch, kv_len_host);
 }
 
+int gpu_attention_layer_set_host_copy_overlap(void *layer, int on) {
+  if (!layer) return GPU_OPS_E_INVALID;
+  as_layer(layer)->SetHostCopyOverlap(on != 0);
+  return GPU_OPS_OK;
+}
+
 int gpu_attention_layer_forward_fused(void *layer, void *out, const void *qkv, const void *qkv_bias, int batch,
                                       int cur_pos, int prev_pos, const int32_t *kv_len_host, gpu_stream_t stream) {
   if (!layer || !out || !qkv || cur_pos < prev_pos || prev_pos < 0) return GPU_OPS_E_INVALID;

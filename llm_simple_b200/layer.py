@@ -14,7 +14,7 @@ EXPORTS = [
     "gpu_attention_layer_decode_ragged", "gpu_attention_layer_set_shared_lens",
     "gpu_attention_layer_forward_host", "gpu_attention_layer_forward_fused", "gpu_attention_layer_cache",
     "gpu_decode_step_create", "gpu_decode_step_destroy", "gpu_decode_step_prepare",
-    "gpu_attention_layer_set_shared_step", "gpu_kv_cache_layout",
+    "gpu_attention_layer_set_shared_step", "gpu_kv_cache_layout", "gpu_attention_layer_set_host_copy_overlap",
 ]
 
 LLAMA2, QWEN2 = 0, 1
@@ -48,6 +48,7 @@ def lib():
         L.gpu_decode_step_destroy.argtypes = [vp]
         L.gpu_decode_step_prepare.argtypes = [vp, vp, i, i, vp]
         L.gpu_attention_layer_set_shared_step.argtypes = [vp, vp]
+        L.gpu_attention_layer_set_host_copy_overlap.argtypes = [vp, i]
         L.gpu_kv_cache_layout.restype = sz
         L.gpu_kv_cache_layout.argtypes = [ctypes.POINTER(ops.AttnDesc), i, i, i, i]
         _ready = True
@@ -140,6 +141,11 @@ class AttentionLayer:
         """step: a DecodeStep prepared for this decode step, or None."""
         self._step = step
         ops._check(lib().gpu_attention_layer_set_shared_step(self.h, step.h if step is not None else None))
+
+    def set_host_copy_overlap(self, on):
+        """False: forward_host copies its input on the caller's stream, behind that stream's earlier
+        work; True (the default): on the layer's own stream, the caller's stream waits for it."""
+        ops._check(lib().gpu_attention_layer_set_host_copy_overlap(self.h, int(bool(on))))
 
     def forward_host(self, out_host, qkv_host, batch, cur_pos, prev_pos, kv_len=None, stream=None):
         lens_ptr = None

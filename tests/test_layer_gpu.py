@@ -114,6 +114,37 @@ def test_host_buffer_prefill_matches_device_prefill(layer):
     b.close()
 
 
+def test_host_buffer_calls_back_to_back_equal_the_strictly_ordered_ones(layer):
+    """A prompt and eight one-token steps through forward_host without a synchronisation in between (the
+    input copies run ahead on the layer's own stream and reuse one staging buffer) give the bits of
+    the same calls with the copies on the caller's stream and a synchronisation after each."""
+    H, kvh, dt, neox, theta, m, max_seq, steps = 12, 2, BF16, True, 1e6, 200, 256, 8
+    width = (H + 2 * kvh) * D
+    rows = [rnd_bits((m, width), dt, 70)] + [rnd_bits((1, width), dt, 71 + i) for i in range(steps)]
+    ins = [torch.from_numpy(r.view(np.int16)).pin_memory() for r in rows]
+    results = []
+    side = torch.cuda.Stream()
+    for overlap in (True, False):
+        k_c = torch.zeros((1, kvh, max_seq, D), dtype=torch.bfloat16, device="cuda")   # caller-owned, adopted
+        v_c = torch.zeros_like(k_c)
+        lay = layer.AttentionLayer(layer.QWEN2, H, kvh, max_seq, 1, dt, theta, neox, layer.HEAD_MAJOR,
+                                   k_cache=k_c, v_cache=v_c)
+        lay.set_host_copy_overlap(overlap)
+        outs = [torch.zeros((r.shape[0], H * D), dtype=torch.int16).pin_memory() for r in rows]
+        pos = 0
+        for x, o in zip(ins, outs):
+            lay.forward_host(o, x, 1, pos + x.shape[0], pos, stream=side if overlap else None)
+            pos += x.shape[0]
+            if not overlap:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        results.append(([o.numpy().copy() for o in outs], host(k_c).copy(), host(v_c).copy()))
+        lay.close()
+    for a, b in zip(results[0][0], results[1][0]):
+        assert np.array_equal(a, b)
+    assert np.array_equal(results[0][1], results[1][1]) and np.array_equal(results[0][2], results[1][2])
+
+
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_fused_projection_row_prefill_then_decode(layer, with_bias):
     """forward_fused on a packed q|k|v row (+ bias row) equals forward on the split, biased tensors bit for bit:
