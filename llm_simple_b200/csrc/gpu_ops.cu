@@ -321,6 +321,14 @@ int rope_append_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, voi
       !aligned16(v_in) || !aligned16(freqs_cis_dev))
     return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
   if (m == 0) return GPU_OPS_OK;
+  // With the sequence as the outermost cache dimension the caches lie cache_seq_stride apart: rows
+  // appended beyond what that stride holds would land in the next sequence's cache (or behind the last).
+  if (!pages && !start_pos_dev && desc->batch > 1 && desc->cache_seq_stride > 0 &&
+      desc->cache_seq_stride >= desc->cache_head_stride && desc->cache_seq_stride >= desc->cache_pos_stride &&
+      (static_cast<long>(start_pos) + m) * desc->n_kv_heads * desc->head_dim > desc->cache_seq_stride)
+    return fail(GPU_OPS_E_INVALID, "positions %d..%ld do not fit the cache (%ld per sequence)", start_pos,
+                static_cast<long>(start_pos) + m - 1,
+                static_cast<long>(desc->cache_seq_stride / (static_cast<long>(desc->n_kv_heads) * desc->head_dim)));
   RopeParams p{};
   int slots = 0;
   if (q_out) {
@@ -819,6 +827,14 @@ int gpu_attn_decode_planned_layer(const gpu_attn_desc *desc, const gpu_kv_pages 
     if (entries > pages->table_stride)
       return fail(GPU_OPS_E_INVALID, "page table rows hold %d entries, %ld needed", pages->table_stride, entries);
   }
+  // Without paging, and with the sequence as the outermost dimension of the cache, the sequences'
+  // caches lie cache_seq_stride apart: a sequence longer than that stride holds would read and
+  // (with an appended token) write the next sequence's memory.
+  if (!pages && desc->batch > 1 && desc->cache_seq_stride >= desc->cache_head_stride &&
+      desc->cache_seq_stride >= desc->cache_pos_stride && desc->cache_seq_stride > 0 &&
+      static_cast<long>(h->max_total) * desc->n_kv_heads * desc->head_dim > desc->cache_seq_stride)
+    return fail(GPU_OPS_E_INVALID, "the plan's longest sequence (%d positions) does not fit the cache (%ld per sequence)",
+                h->max_total, static_cast<long>(desc->cache_seq_stride / (static_cast<long>(desc->n_kv_heads) * desc->head_dim)));
   PlannedDecodeParams p{};
   p.g = geom_from_desc(desc);
   p.out = o_partial ? nullptr : out;

@@ -201,3 +201,10 @@ def test_planned_decode_rejects_bad_arguments(ops):
             ops.gpu_attn_decode_planned_layer(desc, None, plan, t, None, None, t, t, t, t, t, t, None, None, 0)
     with pytest.raises(ops.GpuOpsError):
         ops.DecodePlan(desc, [100, -1], True, 0)
+    # the cache of the descriptor holds 128 positions per sequence: a plan for 128 + the new token does not fit
+    long_plan = ops.DecodePlan(desc, [128, 5], True, 0)
+    long_plan.upload()
+    ws = torch.zeros(max(long_plan.workspace_bytes, 16), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ops.GpuOpsError, match="does not fit the cache"):
+        ops.gpu_attn_decode_planned_layer(desc, None, long_plan, t, None, None, t, t, t, t, t, t, None, ws,
+                                          long_plan.workspace_bytes)

@@ -112,3 +112,16 @@ def test_rope_rejects_bad_arguments(ops):
     with pytest.raises(ops.GpuOpsError):
         ops.gpu_rope_single_layer(x, tab, x, -1, 4, 2, 256, False, FP16)  # negative start
     assert "start_pos" in ops.last_error_string()
+
+
+def test_append_beyond_the_cache_of_a_sequence_is_rejected(ops):
+    """Two sequences with caches of 64 positions: rows 60..67 of a sequence would land in its neighbour's cache."""
+    H, kvh, max_pos, m = 4, 2, 64, 8
+    desc = ops.make_desc(FP16, 2, H, kvh, m, max_pos, layout="head")
+    q = torch.zeros((2, m, H * 128), dtype=torch.float16, device="cuda")
+    kv = torch.zeros((2, m, kvh * 128), dtype=torch.float16, device="cuda")
+    cache = torch.zeros((2, kvh, max_pos, 128), dtype=torch.float16, device="cuda")
+    tab = torch.zeros((max_pos + m, 64, 2), device="cuda")
+    ops.gpu_rope_kv_append_layer(desc, q, cache, cache.clone(), q, kv, kv, tab, None, max_pos - m, m)   # fits exactly
+    with pytest.raises(ops.GpuOpsError, match="do not fit the cache"):
+        ops.gpu_rope_kv_append_layer(desc, q, cache, cache.clone(), q, kv, kv, tab, None, max_pos - m + 4, m)
