@@ -534,6 +534,18 @@ static int prefill_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, 
   if (m <= 0 || offset < 0) return fail(GPU_OPS_E_INVALID, "m %d, offset %d", m, offset);
   if (!aligned16(out) || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache))
     return fail(GPU_OPS_E_INVALID, "tensor pointers must be 16-byte aligned");
+  const long n_pos = static_cast<long>(offset) + m;
+  if (pages) {
+    const long entries = (n_pos + pages->page_size - 1) / pages->page_size;
+    if (entries > pages->table_stride)
+      return fail(GPU_OPS_E_INVALID, "page table rows hold %d entries, %ld needed", pages->table_stride, entries);
+  } else if (desc->batch > 1 && desc->cache_seq_stride > 0 && desc->cache_seq_stride >= desc->cache_head_stride &&
+             desc->cache_seq_stride >= desc->cache_pos_stride &&
+             n_pos * desc->n_kv_heads * desc->head_dim > desc->cache_seq_stride) {
+    // sequence outermost: the caches lie cache_seq_stride apart and cannot hold more positions than that
+    return fail(GPU_OPS_E_INVALID, "%ld positions do not fit the cache (%ld per sequence)", n_pos,
+                static_cast<long>(desc->cache_seq_stride / (static_cast<long>(desc->n_kv_heads) * desc->head_dim)));
+  }
   PrefillParams p{};
   p.g = geom_from_desc(desc);
   p.out = out;

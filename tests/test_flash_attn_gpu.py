@@ -154,3 +154,19 @@ def test_rejects_bad_arguments(ops):
             ops.gpu_flash_attn_layer(x, x, x, x, *args)
     with pytest.raises(ops.GpuOpsError):
         ops.gpu_flash_attn_layer(None, x, x, x, 4, 4, 0, 2, 128, FP16)
+
+
+def test_prefill_over_more_positions_than_a_sequence_caches_is_rejected(ops):
+    """Two sequences with caches of 128 positions: a prefill over 120 + 16 positions would read the neighbour's."""
+    H, kvh, max_pos, m = 4, 2, 128, 16
+    desc = ops.make_desc(FP16, 2, H, kvh, m, max_pos, layout="head")
+    q = torch.zeros((2, m, H * 128), dtype=torch.float16, device="cuda")
+    cache = torch.zeros((2, kvh, max_pos, 128), dtype=torch.float16, device="cuda")
+    ops.gpu_attn_prefill_layer(desc, torch.empty_like(q), q, cache, cache, m, max_pos - m)    # fits exactly
+    with pytest.raises(ops.GpuOpsError, match="do not fit the cache"):
+        ops.gpu_attn_prefill_layer(desc, torch.empty_like(q), q, cache, cache, m, max_pos - m + 8)
+    t = torch.zeros((2, 2), dtype=torch.int32, device="cuda")                                   # 2 pages of 64 per sequence
+    pool = torch.zeros((4, kvh, 64, 128), dtype=torch.float16, device="cuda")
+    with pytest.raises(ops.GpuOpsError, match="page table rows"):
+        ops.gpu_attn_prefill_paged_layer(desc, ops.make_pages(t, 64, kvh * 64 * 128, 4), torch.empty_like(q), q, pool,
+                                         pool, m, max_pos - m + 8)
