@@ -416,6 +416,14 @@ int gpu_attn_set_decode_chunk(int positions);
  * describe the geometry.  Process-wide; for tests and measurements. */
 int gpu_attn_set_prefill_kernel(int which);
 
+/* The tcgen05 prefill kernel starts its CTAs chunk by chunk of (sequence, head)
+ * pairs, and inside a chunk the longest row block of every pair first, so that
+ * the last CTAs to start are the shortest while a chunk's K and V stay in L2
+ * together.  bytes = the K/V a chunk may hold (0 restores the built-in 40 MB,
+ * chosen for the 126 MB L2 of a B200).  Results do not depend on it.
+ * Process-wide tuning knob. */
+int gpu_attn_set_prefill_l2_budget(size_t bytes);
+
 /* Which kernel served the calling thread's last prefill-shaped call: 1 = mma.sync
  * kernel, 2 = tcgen05 kernel, 3 = persistent tcgen05 kernel, 0 = none yet.  The automatic choice falls back to
  * the mma.sync kernel when the tcgen05 kernel's tensor maps cannot describe a

@@ -43,6 +43,11 @@
 #include <mutex>
 #include <type_traits>
 
+// K and V a chunk of (sequence, head) pairs may hold in L2 together (see the CTA order at the launch)
+#ifndef PREFILL_CHUNK_BYTES
+#define PREFILL_CHUNK_BYTES (40L << 20)
+#endif
+
 namespace b200attn {
 
 namespace tc5 {
@@ -79,6 +84,10 @@ struct Params {
   // paged cache: page id of (sequence b, position pos) = page_table[b * table_stride + (pos >> page_shift)]
   const int32_t *page_table;
   int table_stride, page_shift;
+  // CTA order (see the launch): chunk_groups (sequence, head) pairs per chunk, `pad` empty places at
+  // the front of the first chunk, n_heads and a multiplier that divides by it
+  int chunk_groups, pad, n_heads;
+  uint32_t heads_mul;
 };
 
 template <typename T>
@@ -102,7 +111,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
   }
-  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // grid = ((sequence, head) pair within its chunk, row block longest first, chunk): CTAs start in that
+  // order, so a chunk's longest row blocks all start before its shorter ones
+  const int pair = static_cast<int>(blockIdx.z) * p.chunk_groups + static_cast<int>(blockIdx.x) - p.pad;
+  if (pair < 0) return;                        // a padding place of the first chunk
+  const int qb = gridDim.y - 1 - blockIdx.y;
+  const int b = p.heads_mul ? static_cast<int>(__umulhi(static_cast<uint32_t>(pair), p.heads_mul)) : pair / p.n_heads;
+  const int h = pair - b * p.n_heads;
   const int kvh = h / p.group;
   const int row0 = qb * 2 * kBM;                 // first row of tile A; tile B starts kBM later
   const bool has_b = row0 + kBM < p.m;
@@ -559,7 +574,27 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   kp.page_table = p.pg.table;
   kp.table_stride = p.pg.table_stride;
   kp.page_shift = p.pg.page_shift;
-  dim3 grid((p.m + 2 * kBM - 1) / (2 * kBM), g.n_heads, g.batch);
+  // CTA order.  The row blocks of a (sequence, head) pair cost 1, 2, ... , nqb units (causal), and the
+  // hardware starts CTAs in grid order on whichever SM frees up.  Pairs are taken in chunks whose K and V
+  // fit in L2 together; inside a chunk the longest row block of every pair comes first, then the next
+  // longest, so that the pairs still find their K/V in L2 and the last CTAs to start are the shortest
+  // (the partial chunk, if any, goes first).  With pair after pair in full the last pair's longest block
+  // starts near the end and runs alone: at 2 waves of CTAs that is a third of the kernel's time.
+  const int nqb = (p.m + 2 * kBM - 1) / (2 * kBM);
+  const long pairs = static_cast<long>(g.n_heads) * g.batch;
+  const long kv_bytes_per_pair = 2L * p.n * kHeadDim * 2 / g.group;     // K and V, shared by a group's heads
+  long chunk = (p.l2_budget > 0 ? p.l2_budget : PREFILL_CHUNK_BYTES) / (kv_bytes_per_pair > 0 ? kv_bytes_per_pair : 1);
+  chunk = chunk < 1 ? 1 : chunk > pairs ? pairs : chunk;
+  if ((pairs + chunk - 1) / chunk > 65535) chunk = (pairs + 65534) / 65535;
+  const long n_chunks = (pairs + chunk - 1) / chunk;
+  if (nqb > 65535 || chunk > 0x7fffffffL) return cudaErrorNotSupported;
+  kp.chunk_groups = static_cast<int>(chunk);
+  kp.pad = static_cast<int>(n_chunks * chunk - pairs);
+  kp.n_heads = g.n_heads;
+  // floor(pair / n_heads) = (pair * heads_mul) >> 32, exact while pair < 2^32 / n_heads
+  kp.heads_mul = (pairs < (1L << 20) && g.n_heads <= 1024) ? static_cast<uint32_t>((1ULL << 32) / g.n_heads + 1) : 0u;
+  if (g.n_heads == 1) kp.heads_mul = 0u;    // 2^32 + 1 does not fit; the plain division serves
+  dim3 grid(static_cast<unsigned>(chunk), nqb, static_cast<unsigned>(n_chunks));
   // the shared-memory opt-in is a property of (function, device): set it on the first launch per device
   static bool attr_set[2][64] = {};
   int dev = 0;

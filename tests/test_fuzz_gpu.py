@@ -116,3 +116,27 @@ def test_wide_dynamic_range_scores(ops, kernel, dt):
     assert ops.gpu_ops_kernel_status() == 0
     gold = orc.attn(q, k, v, m, n, n - m, 1, H, D, dt, orc.MODE_GOLDEN, threads=8)
     assert_parity(host(out), gold, dt, "wide range")
+
+
+@pytest.mark.parametrize("budget", [1, 200 << 10, 1 << 20, 3 << 20])
+def test_prefill_cta_order_does_not_change_a_bit(ops, budget):
+    """The tcgen05 prefill kernel starts its CTAs in chunks of (sequence, head) pairs sized by an L2 budget:
+    every budget (one pair per chunk, chunks that do not divide the pairs, one chunk) gives the bits of
+    the default, on a batch with several row blocks per pair."""
+    batch, H, kvh, m, offset, dt = 3, 10, 5, 700, 300, BF16
+    n = m + offset
+    q = dev(rnd_bits((batch, m, H * D), dt, 900), dt)
+    kc, vc = dev(rnd_bits((batch, kvh, n, D), dt, 901), dt), dev(rnd_bits((batch, kvh, n, D), dt, 902), dt)
+    desc = ops.make_desc(dt, batch, H, kvh, m, n, layout="head")
+    want, got = torch.empty_like(q), torch.full_like(q, float("nan"))
+    ops.gpu_attn_set_prefill_kernel(2)
+    try:
+        ops.gpu_attn_prefill_layer(desc, want, q, kc, vc, m, offset)
+        ops.gpu_attn_set_prefill_l2_budget(budget)
+        ops.gpu_attn_prefill_layer(desc, got, q, kc, vc, m, offset)
+        torch.cuda.synchronize()
+    finally:
+        ops.gpu_attn_set_prefill_l2_budget(0)
+        ops.gpu_attn_set_prefill_kernel(0)
+    assert ops.gpu_ops_kernel_status() == 0 and ops.gpu_attn_last_prefill_kernel() == 2
+    assert np.array_equal(host(got), host(want))
