@@ -43,6 +43,13 @@
 // lanes) and whether tile counts and ring stages are known to be warp-uniform.
 // Hot code size matters (two alternating copies of the softmax loop cost the
 // non-persistent kernel 9 % on short rows and 2 % on long ones), but not enough.
+// The issuing lane has no slack in either kernel: issuing the MMAs of a product
+// from a rolled loop (three more instructions per MMA) costs 20-25 %.  Unrolling
+// this kernel's tile loop by two, so that every ring stage is a literal as the
+// compiler makes it in the non-persistent kernel, gains 3-10 % on long rows and
+// loses 5 % on short ones.  The non-persistent kernel also starts its CTAs in an
+// order that keeps its tail short (chunks of (sequence, head) pairs, longest row
+// blocks first), which this kernel's item numbering does not follow.
 //
 // The counter: two words {next item, CTAs done} per launch, zero before the
 // launch; the last CTA to finish zeroes them again.  The host hands each stream
@@ -128,8 +135,8 @@ struct Item {
 // descriptors, addresses and coordinates from uniform registers, and loop counters, ring stages and
 // barrier parities stay on the uniform datapath only if what they are derived from is known to be
 // uniform -- which the compiler cannot see for a number read from shared memory or produced by an
-// integer division.  (Measured: without this the MMA-issuing lane needs 750 cycles per 8 MMAs instead
-// of the 512 the tensor pipe takes, and becomes the bottleneck of the kernel.)
+// integer division.  (It is not enough here: the MMA-issuing lane of this kernel still needs 720-760
+// cycles per 8 MMAs where the tensor pipe takes 512; see the status note at the top of the file.)
 __device__ __forceinline__ int uniform(int v) { return __reduce_max_sync(__activemask(), v); }
 // The same for a warp that runs converged: a broadcast from lane 0, the idiom compilers recognise.
 __device__ __forceinline__ int uniform_warp(int v) { return __shfl_sync(0xffffffffu, v, 0); }
