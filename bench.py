@@ -330,15 +330,21 @@ class Env:
     pass
 
 
-def timed_repeats(env, step, steps, repeats=REPEATS, min_total_s=0.0):
+def timed_repeats(env, step, steps, repeats=REPEATS, min_total_s=0.0, queue_behind_ms=0.0):
     """Times `steps` calls of step() as one CUDA-event interval on env.stream, `repeats` times (more
     until min_total_s of device time has been covered); a barrier and a synchronize on both sides of
-    every interval; the maximum over the ranks per interval.  Returns the list of ms per interval."""
+    every interval; the maximum over the ranks per interval.  Returns the list of ms per interval.
+    queue_behind_ms > 0: the interval starts behind a sleep kernel of that length, so that the host has
+    queued the launches by the time the device gets to them and the interval holds device time, not the
+    rate at which this script can issue launches."""
     torch, dist = env.torch, env.dist
     out, total = [], 0.0
     while len(out) < repeats or total < min_total_s * 1e3:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         env.barrier()
+        if queue_behind_ms > 0:
+            with torch.cuda.stream(env.stream):
+                torch.cuda._sleep(int(queue_behind_ms * 1e-3 * 1.9e9))
         e0.record(env.stream)
         for _ in range(steps):
             step()
@@ -864,9 +870,26 @@ def split_kv_leg(env, layers=16, reps=20):
         for _ in range(3):
             step()
         ms_list = timed_repeats(env, step, reps, 3)
-        us = statistics.median(ms_list) * 1e3 / (reps * layers)
+        us_calls = statistics.median(ms_list) * 1e3 / (reps * layers)
+        # The steps are issued layer by layer from this script, several launches each: at these sizes the
+        # interval above holds the script's launch rate.  Again with the launches queued behind a sleep
+        # kernel (fewer steps, so that they fit the launch queue): the device time of the same work.
+        short = max(2, reps // 4)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(short):
+            step()
+        host_ms = (time.perf_counter() - t0) * 1e3
+        torch.cuda.synchronize()
+        host = torch.tensor([host_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(host, op=dist.ReduceOp.MAX)
+        ms_list = timed_repeats(env, step, short, 3, queue_behind_ms=1.5 * float(host.item()) + 1.0)
+        us = statistics.median(ms_list) * 1e3 / (short * layers)
         return {"us_per_layer": us, "gbs": nbytes / (us * 1e-6) / 1e9, "frac_of_hbm_peak_all_ranks":
-                nbytes / (us * 1e-6) / 1e9 / (env.pk["hbm"] * world)}
+                nbytes / (us * 1e-6) / 1e9 / (env.pk["hbm"] * world), "us_per_layer_issued_call_by_call": us_calls,
+                "timing": "launches queued behind a sleep kernel: device time; the call-by-call figure holds the "
+                          "launch rate of this script"}
 
     def golden_layer0():
         """Rank 0: the whole cache of layer 0 from the ranks' slices, then the checker."""
@@ -932,6 +955,12 @@ def split_kv_leg(env, layers=16, reps=20):
     res["nccl_planned_kernel"] = timed(step_planned)
     outs["nccl_planned_kernel"] = bits(out[0][0]).copy()
     dec.close()
+    # and the peer-memory exchange behind the planned decode kernel
+    dec = sharding.SplitKVDecoder(desc, DT_BF16, exchange="peer")
+    state = {"plan": None, "ws": None}
+    res["peer_planned_kernel"] = timed(step_planned)
+    outs["peer_planned_kernel"] = bits(out[0][0]).copy()
+    dec.close()
     res["kernel_status"] = ops.gpu_ops_kernel_status()
     same = bool(np.array_equal(outs["nccl"], outs["peer"]))
     flags = [None] * world
@@ -941,7 +970,9 @@ def split_kv_leg(env, layers=16, reps=20):
                              bit_identical_nccl_vs_peer=all(flags),
                              checked="layer 0: merged output of all ranks' position slices against the checker over "
                                      "the whole 32769-position cache; both exchanges")
-        res["parity_planned_kernel"] = parity_stats(orc, outs["nccl_planned_kernel"], gold, orc.DT_BFLOAT16)
+        res["parity_planned_kernel"] = dict(parity_stats(orc, outs["nccl_planned_kernel"], gold, orc.DT_BFLOAT16),
+                                            bit_identical_nccl_vs_peer=bool(np.array_equal(
+                                                outs["nccl_planned_kernel"], outs["peer_planned_kernel"])))
     return res
 
 

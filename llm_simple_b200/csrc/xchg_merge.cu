@@ -5,9 +5,9 @@
 // log-sum-exp per query head (20 KB for 40 heads), and every rank needs all of
 // them.  Instead of a collective library call between two kernels, ONE kernel per
 // rank does the exchange and the merge:
-//   push blocks  (one per peer)  copy this rank's partial into its slot of the
-//                peer's exchange buffer with plain stores over NVLink, fence at
-//                system scope and release a flag there;
+//   push blocks  (one per peer and four query rows) copy this rank's partial into
+//                its slot of the peer's exchange buffer with plain stores over
+//                NVLink, fence at system scope and release the rows' flags there;
 //   merge blocks (one per query row) wait until every peer's flag in the LOCAL
 //                buffer shows this step, then merge the slots from local memory
 //                (same arithmetic and order as attn_merge_kernel, so the result
@@ -29,6 +29,8 @@ namespace b200attn {
 
 namespace {
 
+constexpr int kPushRows = 4; // rows of 128 floats one push block of 128 threads moves with one float4 each
+
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -43,24 +45,40 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 // Flags: one word per (source rank, query row) in each buffer half, so that a row can be pushed
 // and merged as soon as it exists.
 //
-// grid, partial already merged on this rank (ws_o == nullptr): (world - 1) push blocks, then
-// `rows` merge blocks.  grid, partial still split (ws_o != nullptr): `rows` blocks; each merges
+// grid, partial already merged on this rank (ws_o == nullptr): (world - 1) x ceil(rows / 4) push
+// blocks, then `rows` merge blocks.  grid, partial still split (ws_o != nullptr): `rows` blocks; each merges
 // its row's splits, pushes the row to every peer itself and then waits for the peers' rows.
 // block: 128 threads.
 template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_kernel(XchgParams p) {
   const int tid = threadIdx.x;
   const long n = static_cast<long>(p.rows) * (kHeadDim + 1);
   const bool fused = p.ws_o != nullptr;
-  const int n_push = fused ? 0 : p.world - 1;
+  const int row_groups = (p.rows + kPushRows - 1) / kPushRows;
+  const int n_push = fused ? 0 : (p.world - 1) * row_groups;
   if (static_cast<int>(blockIdx.x) < n_push) {
-    // ---- push: this rank's slot -> the same slot in one peer's buffer
-    const int peer = static_cast<int>(blockIdx.x) < p.rank ? blockIdx.x : blockIdx.x + 1;
+    // ---- push: kPushRows rows of this rank's slot -> the same rows in one peer's buffer, one 16-byte
+    // load and store per thread (a single round trip to local memory), then those rows' flags
+    const int pi = static_cast<int>(blockIdx.x) / row_groups, rg = static_cast<int>(blockIdx.x) % row_groups;
+    const int peer = pi < p.rank ? pi : pi + 1;
+    const int r0 = rg * kPushRows, nr = min(kPushRows, p.rows - r0);
     const float *src = p.slots + static_cast<long>(p.rank) * n;
     float *dst = p.peer_slot[peer];
-    for (long i = tid; i < n; i += blockDim.x) dst[i] = src[i];
+    if (tid < nr * (kHeadDim / 4)) {
+      const long i = static_cast<long>(r0) * kHeadDim + 4 * tid;
+      if ((n & 3) == 0) {           // the ranks' slots lie n floats apart: 16-byte aligned when that is a multiple of 4
+        *reinterpret_cast<float4 *>(dst + i) = __ldcg(reinterpret_cast<const float4 *>(src + i));
+      } else {
+        const float a = __ldcg(src + i), b = __ldcg(src + i + 1), c = __ldcg(src + i + 2), e = __ldcg(src + i + 3);
+        dst[i] = a, dst[i + 1] = b, dst[i + 2] = c, dst[i + 3] = e;
+      }
+    }
+    if (tid < nr) {
+      const long i = static_cast<long>(p.rows) * kHeadDim + r0 + tid;
+      dst[i] = __ldcg(src + i);
+    }
     __threadfence_system();
     __syncthreads();
-    for (int r = tid; r < p.rows; r += blockDim.x) st_release_sys(p.peer_flag[peer] + r, p.epoch);
+    if (tid < nr) st_release_sys(p.peer_flag[peer] + r0 + tid, p.epoch);
     return;
   }
   const int row = blockIdx.x - n_push, d = tid;
@@ -132,7 +150,8 @@ template <typename T> __global__ void __launch_bounds__(128) attn_xchg_merge_ker
 }
 
 cudaError_t launch_attn_xchg_merge(const XchgParams &p, bool bf16, cudaStream_t stream) {
-  const unsigned blocks = static_cast<unsigned>((p.ws_o ? 0 : p.world - 1) + p.rows);
+  const int row_groups = (p.rows + kPushRows - 1) / kPushRows;
+  const unsigned blocks = static_cast<unsigned>((p.ws_o ? 0 : (p.world - 1) * row_groups) + p.rows);
   if (bf16)
     attn_xchg_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(p);
   else

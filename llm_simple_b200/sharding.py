@@ -204,18 +204,27 @@ class SplitKVDecoder:
                      workspace=None):
         """The same step on the planned decode kernel (gpu_attn_decode_planned_layer): the length of this rank's
         slice is known on the host (a serving loop hands out the slices), so the work partition is built from it
-        and the kernel writes (O, LSE) of every query row straight into the all-gather send buffer.  All-gather
-        exchange only.  `plan` / `workspace`: pass the ones of an earlier call with the same local_len to skip
-        rebuilding them (returned by every call)."""
+        and the kernel writes (O, LSE) of every query row straight into the all-gather send buffer or, with the
+        peer exchange, into this rank's slot of the exchange buffer.  `plan` / `workspace`: pass the ones of an
+        earlier call with the same local_len to skip rebuilding them (returned by every call)."""
         from . import ops
-        if self.peer:
-            raise ValueError("step_planned uses the all-gather exchange")
         tail = self.rank == self.world - 1
         if plan is None:
             plan = ops.DecodePlan(self.desc, [int(local_len)] * self.desc.batch, tail)
             plan.upload()
         if workspace is None:
             workspace = self.torch.empty(max(plan.workspace_bytes, 16), dtype=self.torch.uint8, device="cuda")
+        if self.peer:
+            pe = self.peer
+            pe.epoch += 1
+            o_ptr = ops.gpu_attn_xchg_local_slot(pe.local, pe.world, pe.rank, pe.epoch, self.rows)
+            lse_ptr = o_ptr + self.rows * self.desc.head_dim * 4
+            ops.gpu_attn_decode_planned_layer(self.desc, None, plan, None, o_ptr, lse_ptr, q_in, k_in if tail else None,
+                                              v_in if tail else None, k_cache, v_cache, freqs_cis, rope_pos_dev,
+                                              workspace, plan.workspace_bytes)
+            ops.gpu_attn_xchg_merge_layer(out, pe.local, pe.peers, pe.world, pe.rank, pe.epoch, self.rows,
+                                          self.desc.head_dim, self.dt)
+            return plan, workspace
         o_ptr = self.send.data_ptr()
         lse_ptr = o_ptr + self.rows * self.desc.head_dim * 4
         ops.gpu_attn_decode_planned_layer(self.desc, None, plan, None, o_ptr, lse_ptr, q_in, k_in if tail else None,

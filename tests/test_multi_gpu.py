@@ -89,8 +89,16 @@ def _rank_main(rank, world, port, ret):
                          torch.from_numpy(table).cuda(), sl_hi - sl_lo,
                          torch.tensor([total_old], dtype=torch.int32, device="cuda"))
         torch.cuda.synchronize()
+        # and the planned kernel in front of the exchange over peer memory
+        dec_peer = sharding.SplitKVDecoder(desc, dt, exchange="peer")
+        out_pp = torch.empty((1, H * D), dtype=torch.bfloat16, device="cuda")
+        dec_peer.step_planned(out_pp, dev(q[:1], dt), dev(k[:1], dt), dev(v[:1], dt), dev(kl, dt), dev(vl, dt),
+                              torch.from_numpy(table).cuda(), sl_hi - sl_lo,
+                              torch.tensor([total_old], dtype=torch.int32, device="cuda"))
+        torch.cuda.synchronize()
+        dec_peer.close()
         assert ops.gpu_ops_kernel_status() == 0
-        ret[rank] = (sharded, host(out), host(out_p))
+        ret[rank] = (sharded, host(out), host(out_p), host(out_pp))
     finally:
         dist.destroy_process_group()
 
@@ -104,8 +112,8 @@ def test_two_ranks_head_sharding_and_split_kv_exchange():
     mp.spawn(_rank_main, args=(world, port, ret), nprocs=world, join=True)
     dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc = _case()
     single = _decode(ops, dt, H, kvh, neox, lens, max_pos, table, q, k, v, kc, vc)
-    sharded0, split0, planned0 = ret[0]
-    sharded1, split1, planned1 = ret[1]
+    sharded0, split0, planned0, planned_peer0 = ret[0]
+    sharded1, split1, planned1, planned_peer1 = ret[1]
     # head-sharded vs single device: same kernel on disjoint heads.  Where a head's cache is cut
     # between CTAs depends on how many heads share the device, so the sums may be ordered
     # differently: equal within the parity tolerance, and both ranks gathered the same bytes.
@@ -124,6 +132,8 @@ def test_two_ranks_head_sharding_and_split_kv_exchange():
     assert np.array_equal(split0, split1)
     assert_parity(planned0, gold, dt, "rank 0, planned kernel")
     assert np.array_equal(planned0, planned1)
+    # the two exchanges merge the same partials in the same order
+    assert np.array_equal(planned_peer0, planned0) and np.array_equal(planned_peer1, planned0)
 
 
 def _flow_case():

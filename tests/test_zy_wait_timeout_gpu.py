@@ -14,11 +14,12 @@ from tests.gpu_util import BF16, D
 pytestmark = pytest.mark.gpu
 
 
-def test_exchange_wait_runs_out_and_reports(tmp_path):
+@pytest.mark.parametrize("rows", [8, 5])     # whole groups of four rows with 16-byte copies; a ragged group, unaligned slots
+def test_exchange_wait_runs_out_and_reports(tmp_path, rows):
     from llm_simple_b200 import ops
     ops.lib()
     assert ops.gpu_ops_kernel_status() == 0
-    world, rank, rows = 2, 0, 8
+    world, rank = 2, 0
     nbytes = ops.gpu_attn_xchg_buffer_bytes(world, rows)
     local = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     silent_peer = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")       # stands in for rank 1; never written
