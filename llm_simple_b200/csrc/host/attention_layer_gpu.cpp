@@ -320,10 +320,11 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
   cudaStream_t s = ctx.gpu_stream;
   // The input goes up on the layer's own stream, so that it does not queue behind the kernels the
   // caller's stream still holds; a stream under capture keeps everything in its own order.
-  bool overlap = overlap_host_copies_;
+  bool overlap = overlap_host_copies_, capturing_stream = false;
   if (overlap) {
     cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) overlap = false;
+    if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone)
+      overlap = false, capturing_stream = true;
   }
   if (overlap && !copy_stream_) {
     if (cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking) != cudaSuccess ||
@@ -348,6 +349,7 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
   // store them there themselves (the device address of the same bytes) and no copy is queued behind them.
   void *out_dev = staging_out_->data_ptr;
   if (ctx.cur_size == 1 && overlap_host_copies_) {
+    // asked on every call: the buffer behind an address may have been freed and replaced since the last one
     cudaPointerAttributes at{};
     if (cudaPointerGetAttributes(&at, out_host) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer &&
         reinterpret_cast<uintptr_t>(at.devicePointer) % 16 == 0)
@@ -372,8 +374,7 @@ int AttentionLayerGPUImpl::ForwardHost(void *out_host, const void *qkv_host, Inf
   if (overlap_host_copies_) {
     // whichever way this call's input came, the next overlapped copy must wait for these kernels
     if (!in_free_ && cudaEventCreateWithFlags(&in_free_, cudaEventDisableTiming) != cudaSuccess) return GPU_OPS_E_CUDA;
-    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone) {
+    if (!capturing_stream) {
       if (cudaEventRecord(in_free_, s) != cudaSuccess) return GPU_OPS_E_CUDA;
       in_free_recorded_ = true;
     }
