@@ -422,7 +422,7 @@ int gpu_attn_set_prefill_kernel(int which);
  * together.  bytes = the K/V a chunk may hold (0 restores the built-in 40 MB,
  * chosen for the 126 MB L2 of a B200).  Results do not depend on it.
  * Process-wide tuning knob. */
-int gpu_attn_set_prefill_l2_budget(size_t bytes);
+int gpu_attn_set_prefill_l2_window(size_t bytes);
 
 /* Which kernel served the calling thread's last prefill-shaped call: 1 = mma.sync
  * kernel, 2 = tcgen05 kernel, 3 = persistent tcgen05 kernel, 0 = none yet.  The automatic choice falls back to

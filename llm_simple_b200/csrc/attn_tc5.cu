@@ -583,7 +583,7 @@ cudaError_t launch_attn_prefill_tc5(const PrefillParams &p, bool bf16, cudaStrea
   const int nqb = (p.m + 2 * kBM - 1) / (2 * kBM);
   const long pairs = static_cast<long>(g.n_heads) * g.batch;
   const long kv_bytes_per_pair = 2L * p.n * kHeadDim * 2 / g.group;     // K and V, shared by a group's heads
-  long chunk = (p.l2_budget > 0 ? p.l2_budget : PREFILL_CHUNK_BYTES) / (kv_bytes_per_pair > 0 ? kv_bytes_per_pair : 1);
+  long chunk = (p.l2_window > 0 ? p.l2_window : PREFILL_CHUNK_BYTES) / (kv_bytes_per_pair > 0 ? kv_bytes_per_pair : 1);
   chunk = chunk < 1 ? 1 : chunk > pairs ? pairs : chunk;
   if ((pairs + chunk - 1) / chunk > 65535) chunk = (pairs + 65534) / 65535;
   const long n_chunks = (pairs + chunk - 1) / chunk;

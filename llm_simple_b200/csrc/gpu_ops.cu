@@ -23,7 +23,7 @@ thread_local long g_launches = 0;
 thread_local int g_last_prefill_kernel = 0; // 1 mma.sync, 2 tcgen05, 3 tcgen05 persistent
 std::atomic<int> g_decode_chunk{0};
 std::atomic<int> g_prefill_kernel{0};
-std::atomic<long> g_prefill_l2_budget{0};
+std::atomic<long> g_prefill_l2_window{0};
 std::atomic<int> g_decode_early{0};
 
 // caller-registered scratch for the reference-shaped operators, per device
@@ -229,7 +229,7 @@ int ref_attention(void *out, const void *q, const void *k, const void *v, int m,
   p.n = n;
   p.offset = offset;
   p.scale_log2 = scale_log2_of(head_dim);
-  p.l2_budget = g_prefill_l2_budget.load();
+  p.l2_window = g_prefill_l2_window.load();
   return run_prefill(p, bf16, s);
 }
 
@@ -559,7 +559,7 @@ static int prefill_common(const gpu_attn_desc *desc, const gpu_kv_pages *pages, 
   p.offset = offset;
   p.scale_log2 = scale_log2_of(desc->head_dim);
   p.pg = pg;
-  p.l2_budget = g_prefill_l2_budget.load();
+  p.l2_window = g_prefill_l2_window.load();
   return run_prefill(p, desc->dtype == GPU_DT_BFLOAT16, static_cast<cudaStream_t>(stream));
 }
 
@@ -999,9 +999,9 @@ int gpu_attn_set_prefill_kernel(int which) {
   return GPU_OPS_OK;
 }
 
-int gpu_attn_set_prefill_l2_budget(size_t bytes) {
-  if (bytes > (static_cast<size_t>(1) << 40)) return fail(GPU_OPS_E_INVALID, "L2 budget of %zu bytes", bytes);
-  g_prefill_l2_budget.store(static_cast<long>(bytes));
+int gpu_attn_set_prefill_l2_window(size_t bytes) {
+  if (bytes > (static_cast<size_t>(1) << 40)) return fail(GPU_OPS_E_INVALID, "L2 window of %zu bytes", bytes);
+  g_prefill_l2_window.store(static_cast<long>(bytes));
   return GPU_OPS_OK;
 }
 

@@ -205,7 +205,7 @@ struct PrefillParams {
   int m, n, offset;
   float scale_log2;
   KvPaging pg;    // tcgen05 kernel: pages of at least 128 positions
-  long l2_budget; // tcgen05 kernel: bytes of K and V a chunk of (sequence, head) pairs may share in L2; 0 = default
+  long l2_window; // tcgen05 kernel: bytes of K and V a chunk of (sequence, head) pairs may share in L2; 0 = default
 };
 
 cudaError_t launch_attn_prefill_mma(const PrefillParams &p, bool bf16, cudaStream_t stream);

@@ -27,7 +27,7 @@ EXPORTS = [
     "gpu_attn_xchg_buffer_bytes", "gpu_attn_xchg_local_slot", "gpu_attn_xchg_merge_layer",
     "gpu_attn_decode_xchg_layer",
     "gpu_peer_buffer_alloc", "gpu_peer_buffer_open", "gpu_peer_buffer_close", "gpu_peer_buffer_free",
-    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel", "gpu_attn_set_prefill_l2_budget", "gpu_attn_last_prefill_kernel",
+    "gpu_ops_set_workspace", "gpu_attn_set_decode_chunk", "gpu_attn_set_decode_early_prefetch", "gpu_attn_set_prefill_kernel", "gpu_attn_set_prefill_l2_window", "gpu_attn_last_prefill_kernel",
     "gpu_ops_launch_count", "gpu_ops_last_error_string", "gpu_ops_kernel_status", "gpu_ops_clear_kernel_status",
 ]
 
@@ -146,7 +146,7 @@ def lib():
         L.gpu_attn_set_decode_chunk.argtypes = [i]
         L.gpu_attn_set_decode_early_prefetch.argtypes = [i]
         L.gpu_attn_set_prefill_kernel.argtypes = [i]
-        L.gpu_attn_set_prefill_l2_budget.argtypes = [ctypes.c_size_t]
+        L.gpu_attn_set_prefill_l2_window.argtypes = [ctypes.c_size_t]
         L.gpu_ops_launch_count.argtypes = [i]
         L.gpu_ops_launch_count.restype = ctypes.c_long
         L.gpu_ops_last_error_string.restype = ctypes.c_char_p
@@ -412,9 +412,9 @@ def gpu_attn_set_prefill_kernel(which):
     _check(lib().gpu_attn_set_prefill_kernel(which))
 
 
-def gpu_attn_set_prefill_l2_budget(nbytes):
+def gpu_attn_set_prefill_l2_window(nbytes):
     """K/V bytes a chunk of (sequence, head) pairs may share in L2 (CTA order of the tcgen05 prefill kernel); 0 = default."""
-    _check(lib().gpu_attn_set_prefill_l2_budget(nbytes))
+    _check(lib().gpu_attn_set_prefill_l2_window(nbytes))
 
 
 def gpu_attn_last_prefill_kernel():

@@ -120,8 +120,8 @@ def test_wide_dynamic_range_scores(ops, kernel, dt):
 
 @pytest.mark.parametrize("budget", [1, 200 << 10, 1 << 20, 3 << 20])
 def test_prefill_cta_order_does_not_change_a_bit(ops, budget):
-    """The tcgen05 prefill kernel starts its CTAs in chunks of (sequence, head) pairs sized by an L2 budget:
-    every budget (one pair per chunk, chunks that do not divide the pairs, one chunk) gives the bits of
+    """The tcgen05 prefill kernel starts its CTAs in chunks of (sequence, head) pairs sized by an L2 window:
+    every window (one pair per chunk, chunks that do not divide the pairs, one chunk) gives the bits of
     the default, on a batch with several row blocks per pair."""
     batch, H, kvh, m, offset, dt = 3, 10, 5, 700, 300, BF16
     n = m + offset
@@ -132,11 +132,11 @@ def test_prefill_cta_order_does_not_change_a_bit(ops, budget):
     ops.gpu_attn_set_prefill_kernel(2)
     try:
         ops.gpu_attn_prefill_layer(desc, want, q, kc, vc, m, offset)
-        ops.gpu_attn_set_prefill_l2_budget(budget)
+        ops.gpu_attn_set_prefill_l2_window(budget)
         ops.gpu_attn_prefill_layer(desc, got, q, kc, vc, m, offset)
         torch.cuda.synchronize()
     finally:
-        ops.gpu_attn_set_prefill_l2_budget(0)
+        ops.gpu_attn_set_prefill_l2_window(0)
         ops.gpu_attn_set_prefill_kernel(0)
     assert ops.gpu_ops_kernel_status() == 0 and ops.gpu_attn_last_prefill_kernel() == 2
     assert np.array_equal(host(got), host(want))
